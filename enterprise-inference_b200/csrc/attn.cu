@@ -5,8 +5,8 @@
 // (every cached K and V element of the row's context read once; q/out are noise).
 //
 // Data path: the cache layout [block][kv head][block_size][128] makes a 64-token K (or V) tile of
-// one kv head one contiguous 16 KiB run, so a tile is ONE bulk-async copy (cp.async.bulk ->
-// SASS UBLKCP) completing on an mbarrier; a 3-stage ring keeps 64 KiB of KV in flight per CTA and
+// one kv head one contiguous 16 KiB run, so a tile is ONE bulk-async copy (cp.async.bulk)
+// completing on an mbarrier; a 3-stage ring keeps 64 KiB of KV in flight per CTA and
 // two CTAs fit per SM.  One CTA = (row, kv head, split); the G = hq/hkv query heads of the group
 // share every K/V byte fetched (GQA).  Scores, softmax and the P.V accumulation are fp32 (R4 of
 // oracle/decode_oracle.py); the online-softmax running max/sum are kept per head per CTA.
