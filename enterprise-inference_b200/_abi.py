@@ -23,6 +23,23 @@ class ModelCfg(C.Structure):
                [(n, C.c_int32) for n in ("block_size", "max_tokens", "max_blocks_per_seq", "tp_rank", "tp_world")]
 
 
+class StackLayer(C.Structure):
+    """struct b200_stack_layer"""
+    _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "rot_dims", "rot_table", "vrot_table")] + \
+               [("scale", C.c_float)] + [(n, C.c_int32) for n in ("mlp", "experts", "top", "groups", "keep", "ff")]
+
+
+class StackCfg(C.Structure):
+    """struct b200_stack_cfg"""
+    _fields_ = [(n, C.c_int32) for n in ("width", "vocab", "n_layers")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)] + \
+               [(n, C.c_int32) for n in ("f32", "block_size", "max_tokens", "max_blocks_per_seq", "max_logit_rows")]
+
+
+MIXER_ATTENTION, MLP_NONE, MLP_MOE = 1, 0, 1
+(SW_EMBED, SW_FINAL_NORM, SW_HEAD, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_QKV, SW_Q_NORM,
+ SW_K_NORM, SW_O, SW_ROUTER, SW_ROUTER_BIAS, SW_EXPERT_GATE_UP, SW_EXPERT_DOWN) = range(15)
+SW_F32 = {SW_FINAL_NORM, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_Q_NORM, SW_K_NORM, SW_ROUTER_BIAS}
+
 W_EMBED, W_LN1, W_QKV, W_QKV_BIAS, W_O, W_LN2, W_GATE_UP, W_DOWN, W_FINAL_NORM, W_LM_HEAD, W_GATE_UP_INTERLEAVED = range(11)
 
 _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
@@ -79,6 +96,12 @@ SIGNATURES = {
     "b200_advance_decode_rows": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _vp]),
     "b200_allreduce_bf16": (C.c_int, [_vp, _vp, _i64, _vp]),
     "b200_tp_allreduce": (C.c_int, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
+    "b200_stack_create": (C.c_int, [C.POINTER(StackCfg), C.POINTER(StackLayer), C.POINTER(_vp)]),
+    "b200_stack_set_weight": (C.c_int, [_vp, _i32, _i32, _vp, _i64, _i64]),
+    "b200_stack_set_kv_cache": (C.c_int, [_vp, _i32, _vp, _vp, _i64]),
+    "b200_stack_set_rot_table": (C.c_int, [_vp, _i32, _vp, _i64, _i32]),
+    "b200_stack_set_stream_tap": (C.c_int, [_vp, _vp]),
+    "b200_ctx_logits_last_f32": (C.c_int, [_vp, _i32, _vp, _vp]),
 }
 
 _lib = None

@@ -8,8 +8,8 @@ from __future__ import annotations
 import json
 import math
 import os
-from dataclasses import asdict, dataclass
-from typing import Dict, Optional
+from dataclasses import asdict, dataclass, field
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -134,3 +134,173 @@ def rope_cos_sin(cfg: ModelConfig, max_pos: Optional[int] = None) -> torch.Tenso
     t = torch.arange(max_pos or cfg.max_pos, dtype=torch.float32)
     fr = torch.outer(t, inv)
     return torch.cat((fr.cos(), fr.sin()), dim=-1).to(torch.bfloat16)
+
+
+# ---- models described layer by layer ------------------------------------------------------------------------------------
+# The chart's model list is Llama / Qwen2 only; designs whose layers carry their own sizes and mechanisms are read from the
+# layer list of their config.json into the descriptors of include/b200_decode.h (b200_stack_layer).
+
+@dataclass
+class RotarySpec:
+    """Rotation of the leading `dims` dimensions of a head in the interleaved pair layout (2i, 2i+1), pair i turning by
+    position * f_i with f_i = base^(-2i/dims).  With YaRN scaling (factor, original, fast, slow) the frequencies are
+    blended between f_i and f_i / factor by a linear ramp over the pair index and cos/sin are multiplied by
+    0.1 ln(factor) + 1."""
+    base: float
+    dims: int
+    factor: float = 1.0
+    original: int = 0
+    fast: float = 0.0
+    slow: float = 0.0
+    scaled: bool = False
+
+    def key(self) -> tuple:
+        return (self.base, self.dims, self.factor, self.original, self.fast, self.slow, self.scaled)
+
+    def frequencies(self) -> Tuple[torch.Tensor, float]:
+        """(f[dims/2] float64, magnitude factor)."""
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        f = torch.tensor(self.base, dtype=torch.float64) ** (-2.0 * i / self.dims)
+        if not self.scaled:
+            return f, 1.0
+
+        def pair_of(turns: float) -> float:   # the (fractional) pair index whose wavelength makes `turns` turns over `original` positions
+            return self.dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+        lo = max(math.floor(pair_of(self.fast)), 0)
+        hi = min(math.ceil(pair_of(self.slow)), self.dims - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return f / self.factor * ramp + f * (1.0 - ramp), 0.1 * math.log(self.factor) + 1.0
+
+    def table(self, n_pos: int) -> torch.Tensor:
+        """[n_pos][2][dims/2] fp32: cos row and sin row of every position (angles in float64, rounded once)."""
+        f, mag = self.frequencies()
+        a = torch.arange(n_pos, dtype=torch.float64)[:, None] * f[None, :]
+        return torch.stack((a.cos() * mag, a.sin() * mag), dim=1).to(torch.float32).contiguous()
+
+
+@dataclass
+class AttentionSpec:
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: Optional[RotarySpec] = None       # q/k rotation (None: none)
+    value_rot: Optional[RotarySpec] = None  # values rotate by their position, outputs turn back by the query's (None: off)
+
+
+@dataclass
+class MoESpec:
+    experts: int
+    top: int
+    ff: int
+    groups: int = 1
+    keep: int = 1
+
+
+@dataclass
+class StackLayerSpec:
+    mixer: AttentionSpec
+    mlp: Optional[MoESpec] = None
+
+
+@dataclass
+class BopilornConfig:
+    """Bopilorn: decoder-only; every layer is [layer norm, attention, layer norm] + [layer norm, routed experts, layer norm]
+    over an fp32 residual stream.  Attention: grouped-query, RMS norm of q and of k over the whole projection, partial
+    interleaved rotary with YaRN scaling, unit-RMS values rotated by their position with the output turned back, a score
+    scale of its own.  Experts: softmax router with a choice bias, group-limited top-k, unrenormalised weights."""
+    name: str = "bopilorn"
+    width: int = 256
+    vocab: int = 1024
+    embed_scale: float = 1.0
+    norm_eps: float = 1e-5
+    layers: List[StackLayerSpec] = field(default_factory=list)
+    architecture: str = "Bopilorn"
+
+    @property
+    def hidden(self) -> int:
+        return self.width
+
+    @property
+    def n_layers(self) -> int:
+        return len(self.layers)
+
+    def to_dict(self):
+        return asdict(self)
+
+    def decode_params(self) -> int:
+        """Weights one decode row touches (chosen experts only)."""
+        n = self.vocab * self.width
+        for L in self.layers:
+            a = L.mixer
+            n += self.width * (a.heads * a.dim + a.kv_heads * (a.dim + a.vdim)) + a.heads * a.vdim * self.width
+            if L.mlp:
+                n += L.mlp.experts * self.width + L.mlp.top * 3 * L.mlp.ff * self.width
+        return n
+
+    def weight_bytes(self) -> int:
+        n = 2 * self.vocab * self.width
+        for L in self.layers:
+            a = L.mixer
+            n += self.width * (a.heads * a.dim + a.kv_heads * (a.dim + a.vdim)) + a.heads * a.vdim * self.width
+            if L.mlp:
+                n += L.mlp.experts * (self.width + 3 * L.mlp.ff * self.width)
+        return 2 * n
+
+    def kv_bytes_per_token(self, f32: bool = False) -> int:
+        return sum(L.mixer.kv_heads * (L.mixer.dim + L.mixer.vdim) for L in self.layers) * (4 if f32 else 2)
+
+    @staticmethod
+    def from_dict(c: dict, name: str = "bopilorn") -> "BopilornConfig":
+        layers = []
+        for i, l in enumerate(c["layers"]):
+            if l.get("type") != "attention":
+                raise ValueError(f"layer {i}: unsupported mixer type {l.get('type')!r} (this design has 'attention')")
+            m = l["mixer"]
+            rot = vrot = None
+            r = m.get("rot")
+            if r:
+                sc = r.get("scaling") or None
+                rot = RotarySpec(base=float(r["base"]), dims=int(r["dims"]))
+                if sc:
+                    rot = RotarySpec(base=float(r["base"]), dims=int(r["dims"]), factor=float(sc["factor"]),
+                                     original=int(sc["original"]), fast=float(sc["fast"]), slow=float(sc["slow"]), scaled=True)
+                vrot = RotarySpec(base=float(r["base"]), dims=int(m["vdim"]))   # values: every pair, never scaled
+                if rot.dims == 0:
+                    rot = None
+            att = AttentionSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+                                vdim=int(m.get("vdim", m["dim"])), scale=float(m["scale"]), rot=rot, value_rot=vrot)
+            mlp = None
+            f = l.get("mlp")
+            if f:
+                if f.get("kind", "moe") != "moe":
+                    raise ValueError(f"layer {i}: unsupported feed-forward kind {f.get('kind')!r}")
+                ro, g = f["router"], (f["router"].get("groups") or {})
+                mlp = MoESpec(experts=int(ro["experts"]), top=int(ro["top"]), ff=int(f["expert"]["ff"]),
+                              groups=int(g.get("count", 1)), keep=int(g.get("keep", g.get("count", 1))))
+            layers.append(StackLayerSpec(mixer=att, mlp=mlp))
+        return BopilornConfig(name=name, width=int(c["width"]), vocab=int(c["vocab"]),
+                              embed_scale=float((c.get("embedding") or {}).get("scale", 1.0)),
+                              norm_eps=float((c.get("norm") or {}).get("eps", 1e-5)), layers=layers)
+
+
+# config.json "architecture" -> reader.  HF-style configs (model_type) go through from_hf_config.
+ARCHITECTURES = {"Bopilorn": BopilornConfig.from_dict}
+
+
+def load_model_config(path: str):
+    """The model class is chosen by config.json: an `architecture` of the registry above, else an HF decoder config."""
+    with open(os.path.join(path, "config.json")) as f:
+        c = json.load(f)
+    arch = c.get("architecture")
+    if arch is not None:
+        if arch not in ARCHITECTURES:
+            raise ValueError(f"unsupported architecture {arch!r} (known: {sorted(ARCHITECTURES)})")
+        return ARCHITECTURES[arch](c, name=c.get("_name_or_path", path))
+    return from_hf_config(path)
+
+
+def is_stack_config(cfg) -> bool:
+    return hasattr(cfg, "layers") and not isinstance(cfg, ModelConfig)

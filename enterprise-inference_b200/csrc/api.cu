@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "ctx.cuh"
 
 namespace b200 {
 
@@ -110,76 +111,6 @@ __global__ void tp_pack_kernel(const float* __restrict__ mx, const int32_t* __re
 using namespace b200;
 
 // ------------------------------------------------------------------------------------------------
-struct LayerW {
-  const __nv_bfloat16 *ln1 = nullptr, *qkv = nullptr, *qkv_b = nullptr, *o = nullptr, *ln2 = nullptr, *gu = nullptr,
-                      *down = nullptr;
-  bool gu_interleaved = false;  // gu holds 128-row slabs of 64 gate rows + the 64 matching up rows
-};
-
-struct GraphKey {
-  uint64_t parts[16];   // every pointer and size the captured graph baked in
-  bool operator==(const GraphKey& o) const { return memcmp(parts, o.parts, sizeof(parts)) == 0; }
-};
-struct GraphKeyHash {
-  size_t operator()(const GraphKey& k) const {
-    uint64_t h = 0x1234;
-    for (uint64_t v : k.parts) h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
-    return (size_t)h;
-  }
-};
-
-struct b200_ctx {
-  b200_model_cfg cfg;
-  int hq, hkv, inter, vocab_local, qkv_w;  // local (per TP rank) sizes
-  int max_logit_rows;
-  std::vector<LayerW> layers;
-  const __nv_bfloat16 *embed = nullptr, *final_norm = nullptr, *lm_head = nullptr, *cos_sin = nullptr;
-  int64_t max_pos = 0;
-  __nv_bfloat16 *kc = nullptr, *vc = nullptr;
-  int64_t n_blocks = 0;
-  // private device buffers
-  void* pool = nullptr;
-  int64_t pool_bytes = 0;
-  __nv_bfloat16 *x, *res, *normed, *qkv_buf, *attn_out, *gu_buf, *act, *lm_in, *logits;
-  float *sres, *ssq;   // fp32 residual stream [T][h] and its per-slab sums of squares [T][h/128] (norm folded into the linears)
-  void* attn_ws;
-  int64_t attn_ws_bytes;
-  void* lin_ws;
-  int64_t lin_ws_bytes;
-  int32_t* d_meta;
-  int64_t meta_ints;
-  int32_t* d_tokens;
-  float* d_max;
-  float* d_pairs;     // [rows][2] local (max, idx)
-  float* d_gathered;  // [world][rows][2]
-  void* d_sample;     // sampling parameters of the rows, packed (b200_ctx_sample_last)
-  void* d_logprob;    // [rows] chosen ids | [rows] logprob | [rows][32] top ids | [rows][32] top logprobs
-  void* d_adjust;     // packed penalties / logit_bias of the step's rows (b200_ctx_adjust_last)
-  __nv_bfloat16* logits_full;  // TP only: [world][rows][vocab_local], gathered for the sampler
-  // graphs
-  bool graphs = true;
-  std::unordered_map<GraphKey, cudaGraphExec_t, GraphKeyHash> graph_cache;
-  int last_launches = 0;
-  // taps
-  int tap_layer = -1;
-  void *tap_hidden = nullptr, *tap_res = nullptr;
-  // TP
-  ncclComm_t comm = nullptr;
-  // all-reduce over peer memory (allreduce.cu): one IPC-shareable allocation per rank
-  //   [ partial 0 | partial 1 | gather 0 | gather 1 | flag block (2 x 2 x 8 x 128 B) | state (counter[2], ticket[2]) ]
-  char* ar_mem = nullptr;
-  int64_t ar_buf_bytes = 0, ar_total_bytes = 0;
-  char* ar_peer[8] = {};
-  bool ar_ready = false;
-  int gemv_max_t = 0;  // rows <= this use the CUDA-core GEMV; 0: the tcgen05 path serves every T (measured faster)
-  bool pdl = true;
-  bool fuse = true;                    // epilogue fusion (RoPE+KV, SiLU*mul) on the tcgen05 path
-  // Steps of at most this many rows fold the RMSNorms into the linears (0: off).  Measured on 8B: batch 1 3.05 -> 3.00
-  // ms/step; at 64 rows every CTA of a consumer re-normalises 1 MiB of fp32 rows out of L2 and the step slows from 4.6
-  // to 6.3 ms, so the fold stops at the 16-row tile.
-  int fuse_norm_max_t = 16;
-};
-
 static int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 constexpr int64_t kAdjustMaxInts = 4ll << 20;   // 16 MiB: ~1 M (row, token) entries of penalties / logit_bias per step
 constexpr int64_t kArFlagBytes = 2 * 2 * 8 * 128;   // "partial ready" and "rows delivered" flags: [kind][buffer][rank] x 128 B
@@ -220,6 +151,7 @@ extern "C" int b200_ctx_create(const b200_model_cfg* cfg, b200_ctx** out) {
   c->inter = cfg->intermediate / W;
   c->vocab_local = cfg->vocab / W;
   c->qkv_w = (c->hq + 2 * c->hkv) * kHeadDim;
+  c->logits_ld = c->vocab_local;
   c->max_logit_rows = cfg->max_tokens < 512 ? cfg->max_tokens : 512;
   c->layers.resize(cfg->n_layers);
   if (const char* e = getenv("B200_GEMV_MAX_T")) c->gemv_max_t = atoi(e);
@@ -343,6 +275,7 @@ extern "C" int b200_ctx_destroy(b200_ctx* c) {
   if (c->ar_mem) cudaFree(c->ar_mem);
   for (auto& kv : c->graph_cache) cudaGraphExecDestroy(kv.second);
   if (c->comm && nccl().ok) nccl().CommDestroy(c->comm);
+  if (c->stack) stack_destroy(c);
   if (c->pool) cudaFree(c->pool);
   delete c;
   return B200_OK;
@@ -728,17 +661,6 @@ extern "C" int b200_tp_allreduce(b200_ctx* c, int32_t buf_idx, const void* parti
 }
 
 // ---- the step --------------------------------------------------------------------------------------
-struct StepArgs {
-  const int32_t *ids, *positions, *slots, *block_table, *row_to_seq, *ctx_lens, *logit_rows;
-  int bt_stride, T, max_ctx, R;
-  int32_t* out_tokens;
-  void* out_logits;
-  int n_seqs = 0;   // sequences in the step when the caller knows it (host-buffer entry), else 0
-  // host-buffer entry: the tokens the previous step left in the ctx; an id -(j+1) means "row j of those"
-  const int32_t* prev_tokens = nullptr;
-  int n_prev = 0;
-};
-
 static int enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
   const b200_model_cfg& m = c->cfg;
   const int T = a.T, h = m.hidden;
@@ -918,12 +840,17 @@ static int pow2_bucket(int v) {
 
 static int run_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
   const bool pdl_prev = launch_opts().pdl;   // the caller's per-thread setting is restored on every exit
-  B200_REQUIRE(c->embed && c->final_norm && c->lm_head && c->cos_sin && c->kc, B200_ERR_STATE,
-               "decode_step: weights / rope cache / kv cache not all set");
-  for (int l = 0; l < c->cfg.n_layers; ++l) {
-    const LayerW& L = c->layers[l];
-    B200_REQUIRE(L.ln1 && L.qkv && L.o && L.ln2 && L.gu && L.down && (!c->cfg.qkv_bias || L.qkv_b), B200_ERR_STATE,
-                 "decode_step: layer %d weights incomplete", l);
+  if (c->stack) {
+    const int rc0 = stack_ready(c);
+    if (rc0) return rc0;
+  } else {
+    B200_REQUIRE(c->embed && c->final_norm && c->lm_head && c->cos_sin && c->kc, B200_ERR_STATE,
+                 "decode_step: weights / rope cache / kv cache not all set");
+    for (int l = 0; l < c->cfg.n_layers; ++l) {
+      const LayerW& L = c->layers[l];
+      B200_REQUIRE(L.ln1 && L.qkv && L.o && L.ln2 && L.gu && L.down && (!c->cfg.qkv_bias || L.qkv_b), B200_ERR_STATE,
+                   "decode_step: layer %d weights incomplete", l);
+    }
   }
   B200_REQUIRE(a.T > 0 && a.T <= c->cfg.max_tokens, B200_ERR_INVALID, "decode_step: n_tokens=%d outside (0,%d]", a.T,
                c->cfg.max_tokens);
@@ -938,7 +865,7 @@ static int run_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
   int rc = B200_OK;
   if (!use_graph) {
     launch_counter() = 0;
-    rc = enqueue_step(c, a, s);
+    rc = c->stack ? stack_enqueue_step(c, a, s) : enqueue_step(c, a, s);
     c->last_launches = launch_counter();
     launch_opts().pdl = pdl_prev;
     return rc;
@@ -955,7 +882,7 @@ static int run_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
     cudaGraph_t g = nullptr;
     B200_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     launch_counter() = 0;
-    rc = enqueue_step(c, b, s);
+    rc = c->stack ? stack_enqueue_step(c, b, s) : enqueue_step(c, b, s);
     const int n = launch_counter();
     cudaError_t e = cudaStreamEndCapture(s, &g);
     launch_opts().pdl = pdl_prev;
@@ -1017,7 +944,7 @@ extern "C" int b200_ctx_sample_last(b200_ctx* c, int32_t n_rows, const void* hos
     rc = sample_rows(c->logits_full, c->vocab_local, n_rows, c->vocab_local * W, c->vocab_local, n * c->vocab_local,
                      temperature, top_k, top_p, min_p, seeds, draws, c->d_tokens, s);
   } else {
-    rc = sample_rows(c->logits, c->vocab_local, n_rows, c->vocab_local, c->vocab_local, 0, temperature, top_k, top_p, min_p,
+    rc = sample_rows(c->logits, c->logits_ld, n_rows, c->vocab_local, c->vocab_local, 0, temperature, top_k, top_p, min_p,
                      seeds, draws, c->d_tokens, s);
   }
   if (rc) return rc;
@@ -1050,7 +977,7 @@ extern "C" int b200_ctx_adjust_last(b200_ctx* c, int32_t n_rows, const void* hos
   const float* row_params = reinterpret_cast<const float*>(w);
   const int32_t* offsets = w + 3 * n;
   const int32_t* ids = offsets + n + 1;
-  return logit_adjust_rows(c->logits, c->vocab_local, n_rows, c->vocab_local, c->cfg.tp_rank * c->vocab_local, row_params, offsets, ids,
+  return logit_adjust_rows(c->logits, c->logits_ld, n_rows, c->vocab_local, c->cfg.tp_rank * c->vocab_local, row_params, offsets, ids,
                            ids + E, ids + 2 * E, reinterpret_cast<const float*>(ids + 3 * E), s);
 }
 
@@ -1084,7 +1011,7 @@ extern "C" int b200_ctx_logprobs_last(b200_ctx* c, int32_t n_rows, const int32_t
     rc = logprob_rows(c->logits_full, c->vocab_local, n_rows, c->vocab_local * W, c->vocab_local, n * c->vocab_local, d_tok,
                       n_top, d_lp, d_ids, d_tlp, s);
   } else {
-    rc = logprob_rows(c->logits, c->vocab_local, n_rows, c->vocab_local, c->vocab_local, 0, d_tok, n_top, d_lp, d_ids, d_tlp, s);
+    rc = logprob_rows(c->logits, c->logits_ld, n_rows, c->vocab_local, c->vocab_local, 0, d_tok, n_top, d_lp, d_ids, d_tlp, s);
   }
   if (rc) return rc;
   B200_CUDA(cudaMemcpyAsync(host_out, d_lp, (size_t)n * 4 * (1 + 2 * n_top), cudaMemcpyDeviceToHost, s));

@@ -252,4 +252,35 @@ int allreduce_twoshot_rmsnorm(const ArParams& p, int T, __nv_bfloat16* res, cons
 int argmax_rows(const __nv_bfloat16* logits, int64_t ld, int rows, int vocab, int index_offset,
                 int32_t* out_ids, float* out_max, cudaStream_t s);
 
+// ---- mechanisms of models described layer by layer (stack.cu) -------------------------------------------------------
+// fp32 residual stream: scaled embedding rows; bias-free layer norm with the sandwich form (post-norm of a sublayer's
+// output added into the stream, then the pre-norm of the next sublayer) in one kernel
+int embed_scaled(const int32_t* ids, const __nv_bfloat16* table, float* out, int T, int width, int vocab, float scale,
+                 cudaStream_t s, const int32_t* prev = nullptr, int n_prev = 0);
+int layernorm_stream(bool f32, float* x, const void* y, const float* yparts, int n_parts, const float* w_post,
+                     const float* w_next, void* out, const int32_t* rows, int T, int width, float eps, cudaStream_t s);
+// whole-projection RMS norm of q and k, interleaved partial rotation from a cos|sin table, unit-RMS (optionally rotated)
+// values, k/v into the paged cache
+int qk_norm_rotate_cache(bool f32, const void* qkv, const float* qw, const float* kw, const int32_t* positions,
+                         const int32_t* slots, const float* rot, int rot_dims, const float* vrot, float* qout, void* kc,
+                         void* vc, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float eps,
+                         int64_t max_pos, cudaStream_t s);
+int convert_f32_to_bf16(const float* in, __nv_bfloat16* out, int64_t n, cudaStream_t s);
+int convert_bf16_to_f32(const __nv_bfloat16* in, float* out, int64_t n, cudaStream_t s);
+// paged softmax attention for any head sizes (attn_anydim.cu)
+int64_t paged_attn_anydim_workspace_bytes(int T);
+int paged_attn_anydim(bool f32, const float* q, const void* kc, const void* vc, const int32_t* block_table, int bt_stride,
+                      const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, const float* vrot,
+                      int64_t max_pos, void* out, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float scale,
+                      int plan, void* ws, cudaStream_t s);
+// mixture of experts (moe.cu)
+int64_t moe_workspace_bytes(int T, int top, int experts);
+int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
+              int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s);
+int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
+                const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s);
+// true-fp32 CUDA-core linear (linear_simt.cu)
+int linear_simt(bool x_f32, bool y_f32, const void* x, int64_t ldx, const __nv_bfloat16* w, void* y, int64_t ldy, int T, int n_out,
+                int k, cudaStream_t s);
+
 }  // namespace b200

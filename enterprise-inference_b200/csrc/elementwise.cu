@@ -2,6 +2,8 @@
 // (a4+a5), SiLU*mul (a8), greedy argmax (a10).  All are latency/launch bound at decode sizes;
 // their bytes are noise next to the weight stream, so the design goal is: vectorised 16-byte
 // accesses, one pass over the data, rounding points identical to oracle/decode_oracle.py R1/R3/R5/R6.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -295,6 +297,206 @@ __global__ void advance_rows_kernel(int32_t* ids, int32_t* positions, int32_t* s
   slots[t] = block_table[(int64_t)seq * bt_stride + p / block_size] * block_size + p % block_size;
 }
 
+
+// ---------------------------------------------------------------------------------------
+// fp32 residual stream of layer-list models: x[t] = float(table[id]) * scale.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+embed_scaled_kernel(const int32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table, float* __restrict__ out,
+                    int width, int vocab, float scale, const int32_t* prev, int n_prev) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int id = resolve_id(ids[t], vocab, prev, n_prev);
+  const __nv_bfloat16* src = table + (int64_t)id * width;
+  float* dst = out + (int64_t)t * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = __bfloat162float(src[c]) * scale;
+}
+
+// ---------------------------------------------------------------------------------------
+// Layer norm without bias over an fp32 residual stream, with the sandwich form fused: one CTA per row,
+//   (1) y given:   x += (y - mean(y)) / sqrt(var(y) + eps) * w_post   (var = mean of squared deviations; y is either an
+//                  activation row or the sum, in a fixed order, of n_parts fp32 partial rows)
+//   (2) w_next given: out = (x - mean(x)) / sqrt(var(x) + eps) * w_next, the input of the next sublayer.
+// `rows` (nullable) picks the stream rows to read (the logit rows before the output projection).  All arithmetic fp32;
+// the row is staged in shared memory, statistics are two-pass.
+// ---------------------------------------------------------------------------------------
+constexpr int kLnThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();   // red may still be read from the previous call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = 0.f;
+  for (int i = 0; i < nw; ++i) r += red[i];   // same order in every thread
+  return r;
+}
+
+template <typename AT> __device__ __forceinline__ float act_load(const AT* p, int64_t i);
+template <> __device__ __forceinline__ float act_load<float>(const float* p, int64_t i) { return p[i]; }
+template <> __device__ __forceinline__ float act_load<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+template <typename AT> __device__ __forceinline__ void act_store(AT* p, int64_t i, float v);
+template <> __device__ __forceinline__ void act_store<float>(float* p, int64_t i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void act_store<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+template <typename AT>
+__global__ void __launch_bounds__(kLnThreads)
+layernorm_stream_kernel(float* x, const AT* __restrict__ y, const float* __restrict__ yparts, int n_parts,
+                        const float* __restrict__ w_post, const float* __restrict__ w_next, AT* __restrict__ out,
+                        const int32_t* __restrict__ rows, int width, float eps) {
+  extern __shared__ float ln_row[];
+  __shared__ float red[kLnThreads / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int64_t xr = (int64_t)(rows ? rows[t] : t) * width;
+  const float inv_w = 1.0f / (float)width;
+  if (y != nullptr || yparts != nullptr) {
+    float sum = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      float v;
+      if (y != nullptr) {
+        v = act_load<AT>(y, xr + c);
+      } else {
+        v = 0.f;
+        for (int p = 0; p < n_parts; ++p) v += yparts[((int64_t)(rows ? rows[t] : t) * n_parts + p) * width + c];
+      }
+      ln_row[c] = v;
+      sum += v;
+    }
+    const float mean = block_sum(sum, red) * inv_w;
+    float sq = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float d = ln_row[c] - mean;
+      sq = fmaf(d, d, sq);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(sq, red) * inv_w + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float v = x[xr + c] + (ln_row[c] - mean) * rstd * w_post[c];
+      x[xr + c] = v;
+      ln_row[c] = v;
+    }
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) ln_row[c] = x[xr + c];
+  }
+  if (w_next == nullptr) return;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) sum += ln_row[c];
+  const float mean = block_sum(sum, red) * inv_w;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float d = ln_row[c] - mean;
+    sq = fmaf(d, d, sq);
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(sq, red) * inv_w + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    act_store<AT>(out, (int64_t)t * width + c, (ln_row[c] - mean) * rstd * w_next[c]);
+}
+
+// ---------------------------------------------------------------------------------------
+// What follows a fused q|k|v projection whose q and k are RMS-normalised over the WHOLE projection (all heads at once,
+// with a weight), rotated over the leading rot_dims dimensions of each head in the interleaved layout (pair 2i, 2i+1;
+// angles come from a cos|sin table that already carries any frequency scaling and magnitude factor), and whose values are
+// brought to unit RMS per head and, when a value table is given, rotated over all their dimensions by their own
+// position.  q leaves in fp32; k and v go to the paged cache (layout per layer [block][kv head][block_size][dim]).
+// One CTA per token; everything fp32.  Tables: [pos][2][half] fp32 (cos row, then sin row).
+// ---------------------------------------------------------------------------------------
+template <typename AT, typename CT>
+__global__ void __launch_bounds__(256)
+qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict__ qw, const float* __restrict__ kw,
+                            const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
+                            const float* __restrict__ rot, int rot_dims, const float* __restrict__ vrot,
+                            float* __restrict__ qout, CT* kc, CT* vc, int heads, int kv_heads, int dim, int vdim,
+                            int block_size, float eps, int64_t max_pos) {
+  extern __shared__ float row[];
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int qn = heads * dim, kn = kv_heads * dim, vn = kv_heads * vdim, rw = qn + kn + vn;
+  float* vr = row + rw;   // per kv head: 1 / rms of the value
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < rw; c += blockDim.x) {
+    const float v = act_load<AT>(qkv, (int64_t)t * rw + c);
+    row[c] = v;
+    if (c < qn) sq = fmaf(v, v, sq);
+    else if (c < qn + kn) sk = fmaf(v, v, sk);
+  }
+  const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)qn + eps);
+  const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)kn + eps);
+  {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int g = warp; g < kv_heads; g += blockDim.x >> 5) {
+      float s = 0.f;
+      for (int d = lane; d < vdim; d += 32) {
+        const float v = row[qn + kn + g * vdim + d];
+        s = fmaf(v, v, s);
+      }
+      s = warp_sum(s);
+      if (lane == 0) vr[g] = 1.0f / sqrtf(s / (float)vdim + eps);
+    }
+  }
+  __syncthreads();
+  int pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? (int)max_pos - 1 : pos);
+  const int slot = slots[t];
+  const int half = rot_dims >> 1, vhalf = vdim >> 1;
+  const float* rc = rot ? rot + (int64_t)pos * rot_dims : nullptr;        // cos[half] | sin[half]
+  const float* vcs = vrot ? vrot + (int64_t)pos * 2 * vhalf : nullptr;
+  const int64_t blk = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot % block_size : 0;
+  for (int c = threadIdx.x; c < qn + kn; c += blockDim.x) {
+    const bool is_q = c < qn;
+    const int e = is_q ? c : c - qn;
+    const int d = e % dim;
+    const float r = is_q ? rq : rk;
+    const float* w = is_q ? qw : kw;
+    float v = row[c] * r * w[e];
+    if (d < rot_dims && rc) {
+      const int i = d >> 1;
+      const float cs = rc[i], sn = rc[half + i];
+      const float o = row[c ^ 1] * r * w[e ^ 1];   // partner of the pair (dim and the bases are even: c ^ 1 stays in the head)
+      v = (d & 1) ? fmaf(v, cs, o * sn) : fmaf(v, cs, -o * sn);
+    }
+    if (is_q) {
+      qout[(int64_t)t * qn + e] = v;
+    } else if (slot >= 0) {
+      const int g = e / dim;
+      if (sizeof(CT) == 4) reinterpret_cast<float*>(kc)[((blk * kv_heads + g) * block_size + off) * dim + d] = v;
+      else reinterpret_cast<__nv_bfloat16*>(kc)[((blk * kv_heads + g) * block_size + off) * dim + d] = __float2bfloat16_rn(v);
+    }
+  }
+  if (slot < 0) return;
+  for (int c = threadIdx.x; c < vn; c += blockDim.x) {
+    const int g = c / vdim, d = c % vdim;
+    float v = row[qn + kn + c] * vr[g];
+    if (vcs && d < 2 * vhalf) {
+      const int i = d >> 1;
+      const float cs = vcs[i], sn = vcs[vhalf + i];
+      const float o = row[qn + kn + (c ^ 1)] * vr[g];
+      v = (d & 1) ? fmaf(v, cs, o * sn) : fmaf(v, cs, -o * sn);
+    }
+    if (sizeof(CT) == 4) reinterpret_cast<float*>(vc)[((blk * kv_heads + g) * block_size + off) * vdim + d] = v;
+    else reinterpret_cast<__nv_bfloat16*>(vc)[((blk * kv_heads + g) * block_size + off) * vdim + d] = __float2bfloat16_rn(v);
+  }
+}
+
+// fp32 logits -> bf16 copy for the samplers
+__global__ void __launch_bounds__(256)
+f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16_rn(in[i]);
+}
+__global__ void __launch_bounds__(256)
+bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ out, int64_t n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = __bfloat162float(in[i]);
+}
 }  // namespace
 
 int advance_rows(int32_t* ids, int32_t* positions, int32_t* slots, int32_t* ctx_lens, const int32_t* block_table,
@@ -339,6 +541,70 @@ int rmsnorm_stream(const float* sres, const float* ssq, const int32_t* rows, con
   B200_REQUIRE(hidden % 128 == 0, B200_ERR_UNSUPPORTED, "rmsnorm_stream: hidden %% 128 != 0");
   if (R == 0) return B200_OK;
   B200_CUDA(launch(rmsnorm_stream_kernel, dim3(R), dim3(kNormThreads), 0, s, sres, ssq, rows, w, y, hidden, eps));
+  return B200_OK;
+}
+
+int embed_scaled(const int32_t* ids, const __nv_bfloat16* table, float* out, int T, int width, int vocab, float scale,
+                 cudaStream_t s, const int32_t* prev, int n_prev) {
+  if (T == 0) return B200_OK;
+  B200_CUDA(launch(embed_scaled_kernel, dim3(T), dim3(128), 0, s, ids, table, out, width, vocab, scale, prev, n_prev));
+  return B200_OK;
+}
+
+template <typename AT>
+static int layernorm_stream_t(float* x, const void* y, const float* yparts, int n_parts, const float* w_post,
+                              const float* w_next, void* out, const int32_t* rows, int T, int width, float eps, cudaStream_t s) {
+  if (T == 0) return B200_OK;
+  const size_t smem = (size_t)width * 4;
+  B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "layernorm: width %d too large", width);
+  static bool done[64] = {};
+  if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(layernorm_stream_kernel<AT>, 200 * 1024, done));
+  B200_CUDA(launch(layernorm_stream_kernel<AT>, dim3(T), dim3(kLnThreads), smem, s, x, (const AT*)y, yparts, n_parts, w_post,
+                   w_next, (AT*)out, rows, width, eps));
+  return B200_OK;
+}
+int layernorm_stream(bool f32, float* x, const void* y, const float* yparts, int n_parts, const float* w_post,
+                     const float* w_next, void* out, const int32_t* rows, int T, int width, float eps, cudaStream_t s) {
+  B200_REQUIRE(!(y || yparts) || w_post, B200_ERR_INVALID, "layernorm: a sublayer output needs its norm weight");
+  B200_REQUIRE(!w_next || out, B200_ERR_INVALID, "layernorm: no output for the normed rows");
+  return f32 ? layernorm_stream_t<float>(x, y, yparts, n_parts, w_post, w_next, out, rows, T, width, eps, s)
+             : layernorm_stream_t<__nv_bfloat16>(x, y, yparts, n_parts, w_post, w_next, out, rows, T, width, eps, s);
+}
+
+int qk_norm_rotate_cache(bool f32, const void* qkv, const float* qw, const float* kw, const int32_t* positions,
+                         const int32_t* slots, const float* rot, int rot_dims, const float* vrot, float* qout, void* kc,
+                         void* vc, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float eps,
+                         int64_t max_pos, cudaStream_t s) {
+  if (T == 0) return B200_OK;
+  B200_REQUIRE(dim % 2 == 0 && rot_dims % 2 == 0 && rot_dims <= dim && (vrot == nullptr || vdim % 2 == 0), B200_ERR_UNSUPPORTED,
+               "rotation: head sizes must be even (dim %d, rot_dims %d, vdim %d)", dim, rot_dims, vdim);
+  const size_t smem = ((size_t)heads * dim + (size_t)kv_heads * (dim + vdim) + kv_heads) * 4;
+  B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "qkv row of %zu bytes does not fit shared memory", smem);
+  static bool done[2][64] = {};
+  if (f32) {
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(qk_norm_rotate_cache_kernel<float, float>, 200 * 1024, done[0]));
+    B200_CUDA(launch(qk_norm_rotate_cache_kernel<float, float>, dim3(T), dim3(256), smem, s, (const float*)qkv, qw, kw, positions,
+                     slots, rot, rot_dims, vrot, qout, (float*)kc, (float*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos));
+  } else {
+    if (smem > 48 * 1024)
+      B200_CUDA(ensure_dynamic_smem(qk_norm_rotate_cache_kernel<__nv_bfloat16, __nv_bfloat16>, 200 * 1024, done[1]));
+    B200_CUDA(launch(qk_norm_rotate_cache_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), smem, s,
+                     (const __nv_bfloat16*)qkv, qw, kw, positions, slots, rot, rot_dims, vrot, qout, (__nv_bfloat16*)kc,
+                     (__nv_bfloat16*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos));
+  }
+  return B200_OK;
+}
+
+int convert_f32_to_bf16(const float* in, __nv_bfloat16* out, int64_t n, cudaStream_t s) {
+  if (n == 0) return B200_OK;
+  const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)kNumSMs * 8);
+  B200_CUDA(launch(f32_to_bf16_kernel, dim3(grid), dim3(256), 0, s, in, out, n));
+  return B200_OK;
+}
+int convert_bf16_to_f32(const __nv_bfloat16* in, float* out, int64_t n, cudaStream_t s) {
+  if (n == 0) return B200_OK;
+  const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)kNumSMs * 8);
+  B200_CUDA(launch(bf16_to_f32_kernel, dim3(grid), dim3(256), 0, s, in, out, n));
   return B200_OK;
 }
 

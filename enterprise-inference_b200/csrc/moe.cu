@@ -1,0 +1,339 @@
+// Mixture-of-experts feed-forward: a softmax router with a selection bias and group-limited top-k choice, and the chosen
+// experts' gated feed-forward (down(silu(gate x) * (up x))).
+//
+// Router (one CTA per token, fp32 throughout): z = W_r x, s = softmax(z) over all experts; the CHOICE uses s + bias, the
+// mixing weights use s itself, not renormalised.  With groups: the experts form `groups` equal runs of neighbours, a
+// group's score is its largest choice score, only the `keep` best groups stay eligible (the others count as -inf), then
+// the `top` largest eligible choice scores win.  Ties go to the lowest index.
+//
+// Experts: two forms over the same weights ([expert][2 ff][width]: gate rows then up rows; [expert][width][ff]):
+//  * token form (decode-sized steps): one CTA per (token, chosen slot) streams that expert's three matrices once;
+//  * grouped form (prefill-sized steps): tokens are bucketed by expert on the device (deterministic order: by token, then
+//    slot), and one CTA per (expert, tile of 16 of its tokens) streams the expert's weights once for the whole tile.
+// Both write one fp32 partial row per (token, slot), already multiplied by the mixing weight; the consumer (the norm that
+// follows the feed-forward) adds the slots in slot order, so the result does not depend on which form ran or on what else
+// was in the step beyond fp32 rounding.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+template <typename AT> __device__ __forceinline__ float ld_act(const AT* p, int64_t i);
+template <> __device__ __forceinline__ float ld_act<float>(const float* p, int64_t i) { return p[i]; }
+template <> __device__ __forceinline__ float ld_act<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+
+constexpr int kRouteThreads = 128;
+
+// (value, index) arg-max over a warp, ties to the lowest index
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) {
+      v = ov;
+      i = oi;
+    }
+  }
+}
+
+template <typename AT>
+__global__ void __launch_bounds__(kRouteThreads)
+moe_route_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ wr, const float* __restrict__ bias, int width,
+                 int experts, int top, int groups, int keep, int32_t* __restrict__ out_ids, float* __restrict__ out_w) {
+  extern __shared__ float sm[];
+  float* xs = sm;                 // [width]
+  float* sc = xs + width;         // [experts] softmax scores
+  float* ch = sc + experts;       // [experts] choice scores (eligible) / -inf
+  float* gs = ch + experts;       // [groups]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kRouteThreads / 32;
+  for (int c = threadIdx.x; c < width; c += kRouteThreads) xs[c] = ld_act<AT>(x, (int64_t)t * width + c);
+  __syncthreads();
+  for (int e = warp; e < experts; e += nw) {
+    const __nv_bfloat16* w = wr + (int64_t)e * width;
+    float a = 0.f;
+    for (int c = lane; c < width; c += 32) a = fmaf(__bfloat162float(w[c]), xs[c], a);
+    a = warp_sum(a);
+    if (lane == 0) sc[e] = a;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mx = -INFINITY;
+  for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, sc[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < experts; e += 32) sum += expf(sc[e] - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+  for (int e = lane; e < experts; e += 32) {
+    const float s = expf(sc[e] - mx) * inv;
+    sc[e] = s;
+    ch[e] = s + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = experts / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float b = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, ch[e]);
+      gs[g] = b;
+    }
+    __syncwarp();
+    // drop the groups - keep worst groups: pick the keep best, mark them, then mask the rest
+    for (int k = 0; k < keep; ++k) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (bi == 0x7fffffff || v > bv)) {   // +inf marks "already kept"
+          bv = v;
+          bi = g;
+        }
+      }
+      if (bi == 0x7fffffff) bv = -INFINITY;
+      // lanes without a candidate carry (-inf, big index) and lose every tie
+      warp_argmax(bv, bi);
+      __syncwarp();
+      if (lane == 0 && bi != 0x7fffffff) gs[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (gs[e / per] != INFINITY) ch[e] = -INFINITY;
+    __syncwarp();
+  }
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = ch[e];
+      if (!isnan(v) && (bi == 0x7fffffff || v > bv)) {   // NaN marks "already chosen"
+        bv = v;
+        bi = e;
+      }
+    }
+    if (bi == 0x7fffffff) bv = -INFINITY;
+    warp_argmax(bv, bi);
+    __syncwarp();
+    if (lane == 0) {
+      const int e = bi == 0x7fffffff ? 0 : bi;
+      out_ids[(int64_t)t * top + k] = e;
+      out_w[(int64_t)t * top + k] = bi == 0x7fffffff ? 0.f : sc[e];
+      if (bi != 0x7fffffff) ch[e] = __int_as_float(0x7fc00000);
+    }
+    __syncwarp();
+  }
+}
+
+// ---- token form ---------------------------------------------------------------------------------------------------------
+constexpr int kExpThreads = 256;
+
+template <typename AT>
+__global__ void __launch_bounds__(kExpThreads)
+moe_expert_rows_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu, const __nv_bfloat16* __restrict__ w_down,
+                       const int32_t* __restrict__ ids, const float* __restrict__ wts, int width, int ff, int top,
+                       float* __restrict__ parts) {
+  extern __shared__ float sm[];
+  float* xs = sm;            // [width]
+  float* as = xs + width;    // [ff]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, slot = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kExpThreads / 32;
+  const int e = ids[(int64_t)t * top + slot];
+  const float wt = wts[(int64_t)t * top + slot];
+  for (int c = threadIdx.x; c < width; c += kExpThreads) xs[c] = ld_act<AT>(x, (int64_t)t * width + c);
+  __syncthreads();
+  const __nv_bfloat16* wg = w_gu + (int64_t)e * 2 * ff * width;
+  const __nv_bfloat16* wu = wg + (int64_t)ff * width;
+  for (int f = warp; f < ff; f += nw) {
+    const __nv_bfloat16* g = wg + (int64_t)f * width;
+    const __nv_bfloat16* u = wu + (int64_t)f * width;
+    float a = 0.f, b = 0.f;
+    for (int c = lane; c < width; c += 32) {
+      const float xv = xs[c];
+      a = fmaf(__bfloat162float(g[c]), xv, a);
+      b = fmaf(__bfloat162float(u[c]), xv, b);
+    }
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) as[f] = a / (1.0f + expf(-a)) * b;
+  }
+  __syncthreads();
+  const __nv_bfloat16* wd = w_down + (int64_t)e * width * ff;
+  float* dst = parts + ((int64_t)t * top + slot) * width;
+  for (int o = warp; o < width; o += nw) {
+    const __nv_bfloat16* d = wd + (int64_t)o * ff;
+    float a = 0.f;
+    for (int c = lane; c < ff; c += 32) a = fmaf(__bfloat162float(d[c]), as[c], a);
+    a = warp_sum(a);
+    if (lane == 0) dst[o] = a * wt;
+  }
+}
+
+// ---- grouped form -------------------------------------------------------------------------------------------------------
+// Bucketing: counts per expert, exclusive scan, then a stable fill (one thread per expert walks the (token, slot) pairs in
+// order: deterministic lists without atomics on the order).
+__global__ void moe_bucket_kernel(const int32_t* __restrict__ ids, int n_pairs, int experts, int32_t* __restrict__ offsets,
+                                  int32_t* __restrict__ list) {
+  extern __shared__ int32_t cnt[];   // [experts + 1]
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&cnt[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int c = cnt[e];
+      cnt[e] = run;
+      offsets[e] = run;
+      run += c;
+    }
+    cnt[experts] = run;
+    offsets[experts] = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int o = cnt[e];
+    const int end = cnt[e + 1];
+    for (int i = 0; i < n_pairs && o < end; ++i)
+      if (ids[i] == e) list[o++] = i;
+  }
+}
+
+constexpr int kGrpTokens = 16;
+
+template <typename AT>
+__global__ void __launch_bounds__(kExpThreads)
+moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu, const __nv_bfloat16* __restrict__ w_down,
+                          const int32_t* __restrict__ offsets, const int32_t* __restrict__ list, const float* __restrict__ wts,
+                          int width, int ff, int top, float* __restrict__ parts) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int e = blockIdx.y;
+  const int lo = offsets[e] + blockIdx.x * kGrpTokens, hi = min(offsets[e + 1], lo + kGrpTokens);
+  if (lo >= hi) return;
+  const int n = hi - lo;
+  float* xs = sm;                          // [16][width]
+  float* as = xs + kGrpTokens * width;     // [16][ff]
+  __shared__ int pair_of[kGrpTokens];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kExpThreads / 32;
+  if (threadIdx.x < kGrpTokens) pair_of[threadIdx.x] = threadIdx.x < n ? list[lo + threadIdx.x] : -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < kGrpTokens * width; i += kExpThreads) {
+    const int r = i / width, c = i % width;
+    xs[i] = r < n ? ld_act<AT>(x, (int64_t)(pair_of[r] / top) * width + c) : 0.f;
+  }
+  __syncthreads();
+  const __nv_bfloat16* wg = w_gu + (int64_t)e * 2 * ff * width;
+  const __nv_bfloat16* wu = wg + (int64_t)ff * width;
+  for (int f = warp; f < ff; f += nw) {
+    const __nv_bfloat16* g = wg + (int64_t)f * width;
+    const __nv_bfloat16* u = wu + (int64_t)f * width;
+    float a[kGrpTokens], b[kGrpTokens];
+#pragma unroll
+    for (int r = 0; r < kGrpTokens; ++r) a[r] = b[r] = 0.f;
+    for (int c = lane; c < width; c += 32) {
+      const float gv = __bfloat162float(g[c]), uv = __bfloat162float(u[c]);
+#pragma unroll
+      for (int r = 0; r < kGrpTokens; ++r) {
+        const float xv = xs[r * width + c];
+        a[r] = fmaf(gv, xv, a[r]);
+        b[r] = fmaf(uv, xv, b[r]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kGrpTokens; ++r) {
+      const float av = warp_sum(a[r]), bv = warp_sum(b[r]);
+      if (lane == 0) as[r * ff + f] = av / (1.0f + expf(-av)) * bv;
+    }
+  }
+  __syncthreads();
+  const __nv_bfloat16* wd = w_down + (int64_t)e * width * ff;
+  for (int o = warp; o < width; o += nw) {
+    const __nv_bfloat16* d = wd + (int64_t)o * ff;
+    float a[kGrpTokens];
+#pragma unroll
+    for (int r = 0; r < kGrpTokens; ++r) a[r] = 0.f;
+    for (int c = lane; c < ff; c += 32) {
+      const float dv = __bfloat162float(d[c]);
+#pragma unroll
+      for (int r = 0; r < kGrpTokens; ++r) a[r] = fmaf(dv, as[r * ff + c], a[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kGrpTokens; ++r) {
+      const float av = warp_sum(a[r]);
+      if (lane == 0 && r < n) parts[(int64_t)pair_of[r] * width + o] = av * wts[pair_of[r]];
+    }
+  }
+}
+
+}  // namespace
+
+int64_t moe_workspace_bytes(int T, int top, int experts) { return ((int64_t)T * top + experts + 8) * 4; }
+
+int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
+              int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s) {
+  if (T == 0) return B200_OK;
+  B200_REQUIRE(experts > 0 && top > 0 && top <= experts, B200_ERR_INVALID, "router: top %d of %d experts", top, experts);
+  if (groups < 1) groups = 1;
+  B200_REQUIRE(experts % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (experts / groups), B200_ERR_INVALID,
+               "router: %d experts in %d groups, keep %d, top %d", experts, groups, keep, top);
+  const size_t smem = ((size_t)width + 2 * experts + groups) * 4;
+  B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "router: row of %zu bytes does not fit shared memory", smem);
+  static bool done[2][64] = {};
+  if (f32) {
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(moe_route_kernel<float>, 200 * 1024, done[0]));
+    B200_CUDA(launch(moe_route_kernel<float>, dim3(T), dim3(kRouteThreads), smem, s, (const float*)x, w_router, bias, width, experts,
+                     top, groups, keep, out_ids, out_w));
+  } else {
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(moe_route_kernel<__nv_bfloat16>, 200 * 1024, done[1]));
+    B200_CUDA(launch(moe_route_kernel<__nv_bfloat16>, dim3(T), dim3(kRouteThreads), smem, s, (const __nv_bfloat16*)x, w_router,
+                     bias, width, experts, top, groups, keep, out_ids, out_w));
+  }
+  return B200_OK;
+}
+
+template <typename AT>
+static int moe_experts_t(const AT* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids, const float* wts,
+                         int T, int width, int ff, int experts, int top, float* parts, void* ws, bool grouped, cudaStream_t s) {
+  const size_t smem_g = (size_t)kGrpTokens * (width + ff) * 4;
+  if (grouped && ws != nullptr && smem_g <= 200 * 1024) {
+    int32_t* offsets = static_cast<int32_t*>(ws);
+    int32_t* list = offsets + experts + 8;
+    B200_CUDA(launch(moe_bucket_kernel, dim3(1), dim3(256), (size_t)(experts + 1) * 4, s, ids, T * top, experts, offsets, list));
+    static bool done[64] = {};
+    if (smem_g > 48 * 1024) B200_CUDA(ensure_dynamic_smem(moe_expert_grouped_kernel<AT>, 200 * 1024, done));
+    const int tiles = (T * top + kGrpTokens - 1) / kGrpTokens;   // upper bound of any expert's tiles
+    B200_CUDA(launch(moe_expert_grouped_kernel<AT>, dim3(std::min(tiles, (T + kGrpTokens - 1) / kGrpTokens + 1), experts),
+                     dim3(kExpThreads), smem_g, s, x, w_gu, w_down, (const int32_t*)offsets, (const int32_t*)list, wts, width, ff,
+                     top, parts));
+    return B200_OK;
+  }
+  const size_t smem = ((size_t)width + ff) * 4;
+  B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "experts: width %d + ff %d do not fit shared memory", width, ff);
+  static bool done2[64] = {};
+  if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(moe_expert_rows_kernel<AT>, 200 * 1024, done2));
+  B200_CUDA(launch(moe_expert_rows_kernel<AT>, dim3(T, top), dim3(kExpThreads), smem, s, x, w_gu, w_down, ids, wts, width, ff, top,
+                   parts));
+  return B200_OK;
+}
+
+// parts [T][top][width] fp32: the chosen experts' outputs times their mixing weights, one row per (token, slot).
+int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
+                const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s) {
+  if (T == 0) return B200_OK;
+  // an expert is chosen at most once per token, so it has at most T tokens: ceil(T / 16) tiles bound every expert
+  const bool grouped = (int64_t)T * top >= 4 * (int64_t)experts && T >= 64;
+  return f32 ? moe_experts_t<float>((const float*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, grouped, s)
+             : moe_experts_t<__nv_bfloat16>((const __nv_bfloat16*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts,
+                                            ws, grouped, s);
+}
+
+}  // namespace b200

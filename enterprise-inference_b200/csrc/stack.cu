@@ -1,0 +1,392 @@
+// Models described layer by layer (b200_stack_create): construction, weights, per-layer caches and the step that
+// strings the mechanisms together.  The ctx is the one every other entry point takes: the step runs through
+// b200_decode_step[_host] (CUDA graphs, packed host metadata, token feedback), and sampling, log-probabilities and logit
+// adjustment read the same logits buffer as for the fixed decoder stack.
+//
+// Step over T token rows (decode rows and rows of prefill chunks alike):
+//   x = table[id] * embed_scale                                           fp32 residual stream
+//   per layer:  h = LN(x) -> qkv = W_qkv h -> q/k RMS norm over the whole projection, rotation, unit-RMS rotated values,
+//               k/v into the paged cache -> paged attention (+ output rotation) -> y = W_o a
+//               x += LN(y); h = LN(x)            one kernel (sandwich norm)
+//               router -> chosen experts -> per-slot partial rows;  x += LN(sum of slots); h = LN(x) for the next layer
+//   logit rows: LN(x[rows]) -> W_head -> logits (bf16 for the samplers; fp32 mode keeps the unrounded rows too) -> argmax
+#include <math.h>
+#include <stdlib.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "common.cuh"
+#include "ctx.cuh"
+
+namespace b200 {
+
+struct StackLayerW {
+  const float *n_mix_pre = nullptr, *n_mix_post = nullptr, *n_mlp_pre = nullptr, *n_mlp_post = nullptr, *q_norm = nullptr,
+              *k_norm = nullptr, *router_bias = nullptr;
+  const __nv_bfloat16 *qkv = nullptr, *o = nullptr, *router = nullptr, *e_gate_up = nullptr, *e_down = nullptr;
+  void *kc = nullptr, *vc = nullptr;
+};
+
+struct StackModel {
+  b200_stack_cfg cfg;
+  std::vector<b200_stack_layer> layers;
+  std::vector<StackLayerW> w;
+  const __nv_bfloat16 *embed = nullptr, *head = nullptr;
+  const float* final_norm = nullptr;
+  const float* rot[16] = {};
+  int64_t rot_pos[16] = {};
+  int rot_half[16] = {};
+  int64_t n_blocks = 0;
+  int esz = 2;   // bytes per activation element
+  // buffers (inside the ctx pool)
+  float* x = nullptr;
+  void *hn = nullptr, *qkv = nullptr, *attn = nullptr, *y = nullptr, *lm_in = nullptr;
+  float* q = nullptr;
+  int32_t* route_ids = nullptr;
+  float *route_w = nullptr, *parts = nullptr;
+  void *attn_ws = nullptr, *moe_ws = nullptr;
+  float* tap = nullptr;
+};
+
+static int64_t up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+static int qkv_rows(const b200_stack_layer& L) { return L.heads * L.dim + L.kv_heads * (L.dim + L.vdim); }
+
+// bf16 mode: the tcgen05 weight-streaming linear wherever TMA can address the operands, else the CUDA-core tile kernel;
+// fp32 mode: the CUDA-core kernel in true fp32.
+static int stack_linear(b200_ctx* c, const void* x, int64_t ldx, const __nv_bfloat16* w, void* y, int64_t ldy, int T, int n_out,
+                        int k, cudaStream_t s) {
+  const StackModel* M = c->stack;
+  if (M->cfg.f32) return linear_simt(true, true, x, ldx, w, y, ldy, T, n_out, k, s);
+  static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
+  if (tc_env && k % 8 == 0 && ldx % 8 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 && linear_tc_supported(T, n_out, k) &&
+      linear_tc_workspace_bytes(T, n_out, k) <= c->lin_ws_bytes)
+    return linear_tc((const __nv_bfloat16*)x, ldx, w, nullptr, (__nv_bfloat16*)y, ldy, T, n_out, k, c->lin_ws, c->lin_ws_bytes,
+                     nullptr, s);
+  return linear_simt(false, false, x, ldx, w, y, ldy, T, n_out, k, s);
+}
+
+int stack_ready(const b200_ctx* c) {
+  const StackModel* M = c->stack;
+  B200_REQUIRE(M->embed && M->head && M->final_norm, B200_ERR_STATE, "step: embedding / output weights not set");
+  for (size_t l = 0; l < M->layers.size(); ++l) {
+    const b200_stack_layer& L = M->layers[l];
+    const StackLayerW& W = M->w[l];
+    B200_REQUIRE(W.n_mix_pre && W.n_mix_post && W.qkv && W.q_norm && W.k_norm && W.o && W.kc && W.vc, B200_ERR_STATE,
+                 "step: layer %d mixer weights / cache incomplete", (int)l);
+    if (L.mlp == B200_MLP_MOE)
+      B200_REQUIRE(W.n_mlp_pre && W.n_mlp_post && W.router && W.e_gate_up && W.e_down, B200_ERR_STATE,
+                   "step: layer %d feed-forward weights incomplete", (int)l);
+    B200_REQUIRE(L.rot_dims == 0 || (L.rot_table >= 0 && M->rot[L.rot_table] && M->rot_half[L.rot_table] * 2 == L.rot_dims),
+                 B200_ERR_STATE, "step: layer %d rotation table missing or of another size", (int)l);
+    B200_REQUIRE(L.vrot_table < 0 || (M->rot[L.vrot_table] && M->rot_half[L.vrot_table] * 2 == L.vdim), B200_ERR_STATE,
+                 "step: layer %d value rotation table missing or of another size", (int)l);
+  }
+  return B200_OK;
+}
+
+void stack_destroy(b200_ctx* c) {
+  delete c->stack;
+  c->stack = nullptr;
+}
+
+int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
+  StackModel* M = c->stack;
+  const b200_stack_cfg& m = M->cfg;
+  const bool f32 = m.f32 != 0;
+  const int T = a.T, Wd = m.width, nL = m.n_layers;
+  int rc;
+#define STEP(expr)     \
+  do {                 \
+    rc = (expr);       \
+    if (rc) return rc; \
+  } while (0)
+  // prefill-sized steps share K/V tiles between the rows of a run; the run list is built once per step
+  int attn_plan = (a.row_to_seq && T >= 32 && (a.n_seqs > 0 ? T >= 2 * a.n_seqs : true)) ? 1 : 0;
+  static const int plan_env = getenv("B200_STACK_ATTN_RUNS") ? atoi(getenv("B200_STACK_ATTN_RUNS")) : 1;
+  if (!plan_env) attn_plan = 0;
+  STEP(embed_scaled(a.ids, M->embed, M->x, T, Wd, m.vocab, m.embed_scale, s, a.prev_tokens, a.n_prev));
+  STEP(layernorm_stream(f32, M->x, nullptr, nullptr, 0, nullptr, M->w[0].n_mix_pre, M->hn, nullptr, T, Wd, m.norm_eps, s));
+  for (int l = 0; l < nL; ++l) {
+    const b200_stack_layer& L = M->layers[l];
+    const StackLayerW& W = M->w[l];
+    const float* next_pre = l + 1 < nL ? M->w[l + 1].n_mix_pre : nullptr;
+    const int qr = qkv_rows(L);
+    STEP(stack_linear(c, M->hn, Wd, W.qkv, M->qkv, qr, T, qr, Wd, s));
+    const float* rot = L.rot_dims > 0 ? M->rot[L.rot_table] : nullptr;
+    const float* vrot = L.vrot_table >= 0 ? M->rot[L.vrot_table] : nullptr;
+    int64_t max_pos = 1ll << 40;
+    if (rot) max_pos = std::min(max_pos, M->rot_pos[L.rot_table]);
+    if (vrot) max_pos = std::min(max_pos, M->rot_pos[L.vrot_table]);
+    STEP(qk_norm_rotate_cache(f32, M->qkv, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, vrot, M->q, W.kc, W.vc, T,
+                              L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, max_pos, s));
+    STEP(paged_attn_anydim(f32, M->q, W.kc, W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, vrot, max_pos,
+                           M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, attn_plan, M->attn_ws, s));
+    if (attn_plan == 1) attn_plan = 2;
+    STEP(stack_linear(c, M->attn, L.heads * L.vdim, W.o, M->y, Wd, T, Wd, L.heads * L.vdim, s));
+    if (L.mlp == B200_MLP_MOE) {
+      STEP(layernorm_stream(f32, M->x, M->y, nullptr, 0, W.n_mix_post, W.n_mlp_pre, M->hn, nullptr, T, Wd, m.norm_eps, s));
+      STEP(moe_route(f32, M->hn, W.router, W.router_bias, T, Wd, L.experts, L.top, L.groups, L.keep, M->route_ids, M->route_w, s));
+      STEP(moe_experts(f32, M->hn, W.e_gate_up, W.e_down, M->route_ids, M->route_w, T, Wd, L.ff, L.experts, L.top, M->parts,
+                       M->moe_ws, s));
+      STEP(layernorm_stream(f32, M->x, nullptr, M->parts, L.top, W.n_mlp_post, next_pre, M->hn, nullptr, T, Wd, m.norm_eps, s));
+    } else {
+      STEP(layernorm_stream(f32, M->x, M->y, nullptr, 0, W.n_mix_post, next_pre, M->hn, nullptr, T, Wd, m.norm_eps, s));
+    }
+    if (M->tap)
+      B200_CUDA(cudaMemcpyAsync(M->tap + (int64_t)l * T * Wd, M->x, (size_t)T * Wd * 4, cudaMemcpyDeviceToDevice, s));
+  }
+  // logit rows: final norm through the row indirection, output projection
+  STEP(layernorm_stream(f32, M->x, nullptr, nullptr, 0, nullptr, M->final_norm, M->lm_in, a.logit_rows, a.R, Wd, m.norm_eps, s));
+  if (f32) {
+    STEP(linear_simt(true, true, M->lm_in, Wd, M->head, c->logits_f32, c->logits_ld, a.R, m.vocab, Wd, s));
+    STEP(convert_f32_to_bf16(c->logits_f32, c->logits, (int64_t)a.R * c->logits_ld, s));
+  } else {
+    STEP(stack_linear(c, M->lm_in, Wd, M->head, c->logits, c->logits_ld, a.R, m.vocab, Wd, s));
+  }
+  STEP(argmax_rows(c->logits, c->logits_ld, a.R, m.vocab, 0, a.out_tokens, nullptr, s));
+  if (a.out_logits)
+    B200_CUDA(cudaMemcpy2DAsync(a.out_logits, (size_t)m.vocab * 2, c->logits, (size_t)c->logits_ld * 2, (size_t)m.vocab * 2, a.R,
+                                cudaMemcpyDeviceToDevice, s));
+#undef STEP
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_layer* layers, b200_ctx** out) {
+  B200_REQUIRE(cfg && layers && out, B200_ERR_INVALID, "stack_create: null argument");
+  B200_REQUIRE(cfg->width > 0 && cfg->vocab > 0 && cfg->n_layers > 0 && cfg->block_size > 0 && cfg->max_tokens > 0 &&
+                   cfg->max_blocks_per_seq > 0 && cfg->max_logit_rows > 0,
+               B200_ERR_INVALID, "stack_create: bad sizes");
+  int max_qkv = 0, max_q = 0, max_a = 0, max_top = 0, max_exp = 0, max_ff = 0;
+  for (int l = 0; l < cfg->n_layers; ++l) {
+    const b200_stack_layer& L = layers[l];
+    B200_REQUIRE(L.mixer == B200_MIXER_ATTENTION, B200_ERR_UNSUPPORTED, "stack_create: layer %d: unknown mixer %d", l, L.mixer);
+    B200_REQUIRE(L.heads > 0 && L.kv_heads > 0 && L.heads % L.kv_heads == 0 && L.dim > 0 && L.vdim > 0 && L.dim % 2 == 0 &&
+                     L.rot_dims >= 0 && L.rot_dims <= L.dim && L.rot_dims % 2 == 0 && (L.vrot_table < 0 || L.vdim % 2 == 0) &&
+                     L.rot_table < 16 && L.vrot_table < 16,
+                 B200_ERR_INVALID, "stack_create: layer %d: bad attention sizes", l);
+    B200_REQUIRE(L.mlp == B200_MLP_NONE || L.mlp == B200_MLP_MOE, B200_ERR_UNSUPPORTED, "stack_create: layer %d: unknown feed-forward %d", l, L.mlp);
+    if (L.mlp == B200_MLP_MOE) {
+      const int groups = L.groups < 1 ? 1 : L.groups;
+      B200_REQUIRE(L.experts > 0 && L.top > 0 && L.top <= L.experts && L.ff > 0 && L.experts % groups == 0 && L.keep >= 1 &&
+                       L.keep <= groups && L.top <= L.keep * (L.experts / groups),
+                   B200_ERR_INVALID, "stack_create: layer %d: bad router sizes", l);
+      max_top = std::max(max_top, L.top);
+      max_exp = std::max(max_exp, L.experts);
+      max_ff = std::max(max_ff, L.ff);
+    }
+    max_qkv = std::max(max_qkv, qkv_rows(L));
+    max_q = std::max(max_q, L.heads * L.dim);
+    max_a = std::max(max_a, L.heads * L.vdim);
+  }
+  b200_ctx* c = new b200_ctx();
+  StackModel* M = new StackModel();
+  c->stack = M;
+  M->cfg = *cfg;
+  M->layers.assign(layers, layers + cfg->n_layers);
+  M->w.resize(cfg->n_layers);
+  M->esz = cfg->f32 ? 4 : 2;
+  b200_model_cfg& mc = c->cfg;
+  memset(&mc, 0, sizeof(mc));
+  mc.hidden = cfg->width;
+  mc.n_layers = cfg->n_layers;
+  mc.vocab = cfg->vocab;
+  mc.rms_eps = cfg->norm_eps;
+  mc.block_size = cfg->block_size;
+  mc.max_tokens = cfg->max_tokens;
+  mc.max_blocks_per_seq = cfg->max_blocks_per_seq;
+  mc.tp_rank = 0;
+  mc.tp_world = 1;
+  c->hq = c->hkv = c->inter = c->qkv_w = 0;
+  c->vocab_local = cfg->vocab;
+  c->logits_ld = (int)up(cfg->vocab, 8);
+  c->max_logit_rows = std::min(cfg->max_logit_rows, cfg->max_tokens);
+  if (const char* e = getenv("B200_GRAPHS")) c->graphs = atoi(e) != 0;
+  if (const char* e = getenv("B200_PDL")) c->pdl = atoi(e) != 0;
+  c->x = c->res = c->normed = c->qkv_buf = c->attn_out = c->gu_buf = c->act = c->lm_in = nullptr;
+  c->sres = c->ssq = nullptr;
+  c->attn_ws = nullptr;
+  c->attn_ws_bytes = 0;
+  c->d_pairs = c->d_gathered = nullptr;
+  c->logits_full = nullptr;
+
+  const int64_t T = cfg->max_tokens, Wd = cfg->width, R = c->max_logit_rows, es = M->esz;
+  int64_t lw = 0;
+  if (!cfg->f32) {
+    // the shapes of this model's linears over the row counts where the tcgen05 plan changes
+    std::vector<std::pair<int, int>> shapes;   // (n_out, k)
+    for (int l = 0; l < cfg->n_layers; ++l) {
+      shapes.push_back({qkv_rows(layers[l]), (int)Wd});
+      shapes.push_back({(int)Wd, layers[l].heads * layers[l].vdim});
+    }
+    for (auto& sh : shapes) {
+      if (sh.second % 8) continue;
+      for (int t = 1; t <= T; t = (t < 16 ? 16 : (t % 2 == 0 ? t + 1 : (t - 1) * 2)))
+        lw = std::max<int64_t>(lw, linear_tc_workspace_bytes(t, sh.first, sh.second));
+      lw = std::max<int64_t>(lw, linear_tc_workspace_bytes((int)T, sh.first, sh.second));
+    }
+    if (Wd % 8 == 0) {
+      for (int t = 1; t <= R; t = (t < 16 ? 16 : (t % 2 == 0 ? t + 1 : (t - 1) * 2)))
+        lw = std::max<int64_t>(lw, linear_tc_workspace_bytes(t, cfg->vocab, (int)Wd));
+      lw = std::max<int64_t>(lw, linear_tc_workspace_bytes((int)R, cfg->vocab, (int)Wd));
+    }
+  }
+  c->lin_ws_bytes = std::max<int64_t>(lw, 64 * 1024);
+  c->meta_ints = 6 * T + T * cfg->max_blocks_per_seq;
+  const int64_t attn_ws_bytes = paged_attn_anydim_workspace_bytes((int)T);
+  const int64_t moe_ws_bytes = max_top ? moe_workspace_bytes((int)T, max_top, max_exp) : 16;
+
+  struct Item {
+    void** p;
+    int64_t bytes;
+  };
+  std::vector<Item> items = {
+      {(void**)&M->x, T * Wd * 4},
+      {(void**)&M->hn, T * Wd * es},
+      {(void**)&M->qkv, T * max_qkv * es},
+      {(void**)&M->q, T * max_q * 4},
+      {(void**)&M->attn, T * max_a * es},
+      {(void**)&M->y, T * Wd * es},
+      {(void**)&M->route_ids, T * std::max(max_top, 1) * 4},
+      {(void**)&M->route_w, T * std::max(max_top, 1) * 4},
+      {(void**)&M->parts, T * std::max(max_top, 1) * Wd * 4},
+      {(void**)&M->lm_in, R * Wd * es},
+      {(void**)&M->attn_ws, attn_ws_bytes},
+      {(void**)&M->moe_ws, moe_ws_bytes},
+      {(void**)&c->logits, R * (int64_t)c->logits_ld * 2},
+      {(void**)&c->logits_f32, cfg->f32 ? R * (int64_t)c->logits_ld * 4 : 16},
+      {(void**)&c->lin_ws, c->lin_ws_bytes},
+      {(void**)&c->d_meta, c->meta_ints * 4},
+      {(void**)&c->d_tokens, R * 4},
+      {(void**)&c->d_max, R * 4},
+      {(void**)&c->d_sample, R * 40},
+      {(void**)&c->d_logprob, R * (8 + 32 * 8)},
+      {(void**)&c->d_adjust, (4ll << 20) * 4},
+  };
+  (void)max_ff;
+  int64_t total = 0;
+  for (auto& it : items) total += up(std::max<int64_t>(it.bytes, 16), 1024);
+  cudaError_t e = cudaMalloc(&c->pool, total);
+  if (e == cudaSuccess) e = cudaMemset(c->pool, 0, total);
+  if (e != cudaSuccess) {
+    if (c->pool) cudaFree(c->pool);
+    delete M;
+    delete c;
+    return cuda_fail(e, "cudaMalloc(ctx pool)", __FILE__, __LINE__);
+  }
+  c->pool_bytes = total;
+  int64_t off = 0;
+  for (auto& it : items) {
+    *it.p = static_cast<char*>(c->pool) + off;
+    off += up(std::max<int64_t>(it.bytes, 16), 1024);
+  }
+  if (!cfg->f32) c->logits_f32 = nullptr;
+  *out = c;
+  return B200_OK;
+}
+
+extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, const void* w, int64_t rows, int64_t cols) {
+  B200_REQUIRE(c && c->stack && w, B200_ERR_INVALID, "stack_set_weight: null argument or not a layer-list ctx");
+  B200_REQUIRE(reinterpret_cast<uintptr_t>(w) % 16 == 0, B200_ERR_INVALID, "stack_set_weight: pointer not 16-byte aligned");
+  StackModel* M = c->stack;
+  const int64_t Wd = M->cfg.width, V = M->cfg.vocab;
+  const bool global = kind == B200_SW_EMBED || kind == B200_SW_FINAL_NORM || kind == B200_SW_HEAD;
+  if (!global) B200_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, B200_ERR_INVALID, "stack_set_weight: layer %d out of range", layer);
+  const b200_stack_layer L = global ? b200_stack_layer{} : M->layers[layer];
+  int64_t er = 0, ec = 1;
+  switch (kind) {
+    case B200_SW_EMBED: case B200_SW_HEAD: er = V; ec = Wd; break;
+    case B200_SW_FINAL_NORM: case B200_SW_NORM_MIX_PRE: case B200_SW_NORM_MIX_POST: case B200_SW_NORM_MLP_PRE:
+    case B200_SW_NORM_MLP_POST: er = Wd; break;
+    case B200_SW_QKV: er = qkv_rows(L); ec = Wd; break;
+    case B200_SW_Q_NORM: er = (int64_t)L.heads * L.dim; break;
+    case B200_SW_K_NORM: er = (int64_t)L.kv_heads * L.dim; break;
+    case B200_SW_O: er = Wd; ec = (int64_t)L.heads * L.vdim; break;
+    case B200_SW_ROUTER: er = L.experts; ec = Wd; break;
+    case B200_SW_ROUTER_BIAS: er = L.experts; break;
+    case B200_SW_EXPERT_GATE_UP: er = (int64_t)L.experts * 2 * L.ff; ec = Wd; break;
+    case B200_SW_EXPERT_DOWN: er = (int64_t)L.experts * Wd; ec = L.ff; break;
+    default: B200_REQUIRE(false, B200_ERR_INVALID, "stack_set_weight: unknown kind %d", kind);
+  }
+  B200_REQUIRE(rows == er && cols == ec, B200_ERR_INVALID, "stack_set_weight: kind %d of layer %d expects [%lld,%lld], got [%lld,%lld]",
+               kind, layer, (long long)er, (long long)ec, (long long)rows, (long long)cols);
+  if (kind >= B200_SW_ROUTER && kind != B200_SW_ROUTER_BIAS)
+    B200_REQUIRE(L.mlp == B200_MLP_MOE, B200_ERR_INVALID, "stack_set_weight: layer %d has no routed experts", layer);
+  const float* f = static_cast<const float*>(w);
+  const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(w);
+  switch (kind) {
+    case B200_SW_EMBED: M->embed = b; break;
+    case B200_SW_HEAD: M->head = b; break;
+    case B200_SW_FINAL_NORM: M->final_norm = f; break;
+    case B200_SW_NORM_MIX_PRE: M->w[layer].n_mix_pre = f; break;
+    case B200_SW_NORM_MIX_POST: M->w[layer].n_mix_post = f; break;
+    case B200_SW_NORM_MLP_PRE: M->w[layer].n_mlp_pre = f; break;
+    case B200_SW_NORM_MLP_POST: M->w[layer].n_mlp_post = f; break;
+    case B200_SW_QKV: M->w[layer].qkv = b; break;
+    case B200_SW_Q_NORM: M->w[layer].q_norm = f; break;
+    case B200_SW_K_NORM: M->w[layer].k_norm = f; break;
+    case B200_SW_O: M->w[layer].o = b; break;
+    case B200_SW_ROUTER: M->w[layer].router = b; break;
+    case B200_SW_ROUTER_BIAS: M->w[layer].router_bias = f; break;
+    case B200_SW_EXPERT_GATE_UP: M->w[layer].e_gate_up = b; break;
+    case B200_SW_EXPERT_DOWN: M->w[layer].e_down = b; break;
+  }
+  return B200_OK;
+}
+
+extern "C" int b200_stack_set_kv_cache(b200_ctx* c, int32_t layer, void* k_cache, void* v_cache, int64_t n_blocks) {
+  B200_REQUIRE(c && c->stack && k_cache && v_cache && n_blocks > 0, B200_ERR_INVALID, "stack_set_kv_cache: bad argument");
+  StackModel* M = c->stack;
+  B200_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, B200_ERR_INVALID, "stack_set_kv_cache: layer %d out of range", layer);
+  B200_REQUIRE(M->n_blocks == 0 || M->n_blocks == n_blocks, B200_ERR_INVALID, "stack_set_kv_cache: every layer needs the same block count");
+  M->n_blocks = n_blocks;
+  c->n_blocks = n_blocks;
+  M->w[layer].kc = k_cache;
+  M->w[layer].vc = v_cache;
+  return B200_OK;
+}
+
+extern "C" int b200_stack_set_rot_table(b200_ctx* c, int32_t index, const float* table, int64_t n_pos, int32_t half) {
+  B200_REQUIRE(c && c->stack && table && index >= 0 && index < 16 && n_pos > 0 && half > 0, B200_ERR_INVALID,
+               "stack_set_rot_table: bad argument");
+  c->stack->rot[index] = table;
+  c->stack->rot_pos[index] = n_pos;
+  c->stack->rot_half[index] = half;
+  return B200_OK;
+}
+
+extern "C" int b200_stack_set_stream_tap(b200_ctx* c, float* out) {
+  B200_REQUIRE(c && c->stack, B200_ERR_INVALID, "stack_set_stream_tap: not a layer-list ctx");
+  c->stack->tap = out;
+  c->tap_layer = out ? (1 << 30) : -1;   // a set tap turns graph replay off (run_step)
+  return B200_OK;
+}
+
+extern "C" int b200_ctx_logits_last_f32(b200_ctx* c, int32_t n_rows, float* host_out, void* stream) {
+  B200_REQUIRE(c && host_out, B200_ERR_INVALID, "logits_last_f32: null argument");
+  B200_REQUIRE(c->cfg.tp_world == 1, B200_ERR_UNSUPPORTED, "logits_last_f32: one GPU only");
+  B200_REQUIRE(n_rows > 0 && n_rows <= c->max_logit_rows, B200_ERR_INVALID, "logits_last_f32: n_rows=%d outside (0,%d]", n_rows,
+               c->max_logit_rows);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int V = c->vocab_local, ld = c->logits_ld;
+  if (c->logits_f32) {
+    B200_CUDA(cudaMemcpy2DAsync(host_out, (size_t)V * 4, c->logits_f32, (size_t)ld * 4, (size_t)V * 4, n_rows, cudaMemcpyDeviceToHost, s));
+    return B200_OK;
+  }
+  // widen on the device into the logit-adjust scratch (16 MiB), in slices when the rows exceed it
+  float* tmp = static_cast<float*>(c->d_adjust);
+  const int64_t cap_rows = std::max<int64_t>((4ll << 20) / ld, 1);
+  B200_REQUIRE((int64_t)ld <= (4ll << 20), B200_ERR_UNSUPPORTED, "logits_last_f32: vocabulary too large for the scratch");
+  for (int64_t r0 = 0; r0 < n_rows; r0 += cap_rows) {
+    const int64_t nr = std::min<int64_t>(cap_rows, n_rows - r0);
+    int rc = convert_bf16_to_f32(c->logits + r0 * ld, tmp, nr * ld, s);
+    if (rc) return rc;
+    B200_CUDA(cudaMemcpy2DAsync(host_out + r0 * V, (size_t)V * 4, tmp, (size_t)ld * 4, (size_t)V * 4, nr, cudaMemcpyDeviceToHost, s));
+  }
+  return B200_OK;
+}

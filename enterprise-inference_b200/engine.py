@@ -121,6 +121,9 @@ class Scheduled:
     req: Request
     n_new: int          # token rows this step
     samples: bool       # the last row produces a token
+    # rows of this step (0 .. n_new-1) whose logits are kept besides: scoring given text (prompt log-probabilities, trace
+    # replay).  None: only the sampling row.
+    logit_offsets: Optional[List[int]] = None
 
 
 class Scheduler:
@@ -244,6 +247,33 @@ class Scheduler:
             budget -= n_new
         return out
 
+    def schedule_given(self, items) -> List[Scheduled]:
+        """A step whose composition the caller dictates: items = [(request, n_new rows, logit offsets)].  Exactly these rows
+        run, in this order; nothing is sampled (the caller feeds the tokens).  Requests still waiting are admitted; blocks
+        come from the same allocator as in schedule(), but nothing is preempted: a step that does not fit raises OutOfBlocks
+        before any block is taken."""
+        need = 0
+        for req, n_new, _ in items:
+            if n_new <= 0 or req.n_computed + n_new > req.n_total:
+                raise ValueError(f"{req.request_id}: {n_new} new rows from {req.n_computed} of {req.n_total} tokens")
+            if req.n_computed + n_new > self.max_model_len:
+                raise ValueError(f"{req.request_id}: exceeds max-model-len {self.max_model_len}")
+            need += max(self.blocks.blocks_needed(req.n_computed + n_new) - len(req.block_table), 0)
+        if need > len(self.blocks.free):
+            raise OutOfBlocks(f"need {need} blocks, {len(self.blocks.free)} free")
+        if sum(n for _, n, _ in items) > self.max_tokens:
+            raise ValueError(f"step of {sum(n for _, n, _ in items)} rows exceeds the token budget {self.max_tokens}")
+        out: List[Scheduled] = []
+        for req, n_new, offsets in items:
+            if req in self.waiting:
+                if len(self.running) >= self.max_seqs:
+                    raise ValueError(f"more than {self.max_seqs} live sequences")
+                self.waiting.remove(req)
+                self.running.append(req)
+            self._grow(req, req.n_computed + n_new)
+            out.append(Scheduled(req, n_new, False, logit_offsets=list(offsets or [])))
+        return out
+
     def _preempt(self, req: Request) -> None:
         self.running.remove(req)
         self._release(req)
@@ -253,7 +283,7 @@ class Scheduler:
     def build_batch(self, sched: List[Scheduled]) -> StepBatch:
         bs = self.blocks.block_size
         n = len(sched)
-        if all(s.n_new == 1 and s.samples for s in sched):
+        if all(s.n_new == 1 and s.samples and s.logit_offsets is None for s in sched):
             # decode fast path: one row per sequence, vectorised
             rows = np.fromiter((s.req.row for s in sched), dtype=np.int64, count=n)
             pos = np.fromiter((s.req.n_computed for s in sched), dtype=np.int32, count=n)
@@ -272,7 +302,10 @@ class Scheduler:
                 b.slots.append(r.block_table[p // bs] * bs + p % bs)
                 b.ctx_lens.append(p + 1)
                 b.row_to_seq.append(si)
-            if s.samples:
+            if s.logit_offsets is not None:
+                base = len(b.ids) - s.n_new
+                b.logit_rows.extend(base + o for o in s.logit_offsets)
+            elif s.samples:
                 b.logit_rows.append(len(b.ids) - 1)
             b.block_tables.append(r.block_table)
         return b
@@ -467,6 +500,21 @@ class LLMEngine:
         for r in done:
             self._forget(r.request_id)
         return done + self._take_failed()
+
+    def step_given(self, items) -> int:
+        """One synchronous step over exactly the given rows (Scheduler.schedule_given); returns the number of logit rows the
+        step kept, in the order of the items and of their offsets: read them with runner.logits_last / logprobs_last."""
+        while self._inflight is not None:
+            self._resolve_inflight()
+        sched = self.scheduler.schedule_given(items)
+        batch = self.scheduler.build_batch(sched)
+        n_rows = len(batch.logit_rows)
+        if not n_rows:   # the ABI wants one logit row
+            batch.logit_rows.append(batch.n_tokens - 1)
+        self.runner.step(batch)
+        self.steps += 1
+        self.scheduler.commit(sched, [])
+        return n_rows
 
     def generate(self, prompts: List[List[int]], max_tokens: int, ignore_eos: bool = True) -> List[List[int]]:
         reqs = [Request(f"gen-{i}", list(p), max_tokens=max_tokens, ignore_eos=ignore_eos) for i, p in enumerate(prompts)]

@@ -88,6 +88,10 @@ class ModelRunner:
         self.cos_sin = rope_cos_sin(cfg, max(max_model_len, 16)).to(self.device)
         _abi.check(self.lib.b200_set_rope_cache(self.ctx, self.cos_sin.data_ptr(), self.cos_sin.shape[0]))
 
+        self._alloc_host_buffers()
+
+    def _alloc_host_buffers(self, max_logit_rows: int = 512):
+        max_tokens = self.max_tokens
         self._weights: List[torch.Tensor] = []   # keeps the borrowed device tensors alive
         meta_ints = 6 * max_tokens + max_tokens * self.max_blocks_per_seq
         # two pinned (metadata, tokens) pairs: step_async alternates them, so the host can pack step n+1 while the
@@ -101,7 +105,7 @@ class ModelRunner:
         self._h_out_np = self._h_out.numpy()
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
-        self.max_logit_rows = min(max_tokens, 512)
+        self.max_logit_rows = min(max_tokens, max_logit_rows)
         self._h_sample = torch.zeros(self.max_logit_rows * 32, dtype=torch.uint8).pin_memory()
         self._h_sample_np = self._h_sample.numpy()
         self._h_lp_tok = torch.zeros(self.max_logit_rows, dtype=torch.int32).pin_memory()
@@ -349,6 +353,17 @@ class ModelRunner:
         tlp = out[n + n * n_top:n + 2 * n * n_top].reshape(n, n_top).copy()
         return lp, ids, tlp
 
+    def logits_last(self, n_rows: int) -> np.ndarray:
+        """The logit rows of the LAST step as fp32 [n_rows, vocab] (a copy).  A ctx in 32-bit mode returns its unrounded logits."""
+        if not 0 < n_rows <= self.max_logit_rows:
+            raise ValueError(f"logits_last: {n_rows} rows outside (0, {self.max_logit_rows}]")
+        V = self.cfg.vocab
+        if getattr(self, "_h_logits", None) is None or self._h_logits.numel() < n_rows * V:
+            self._h_logits = torch.empty(max(n_rows, 64) * V, dtype=torch.float32).pin_memory()
+        _abi.check(self.lib.b200_ctx_logits_last_f32(self.ctx, n_rows, self._h_logits.data_ptr(), self.stream.cuda_stream))
+        self.stream.synchronize()
+        return self._h_logits.numpy()[:n_rows * V].reshape(n_rows, V).copy()
+
     def last_step_launches(self) -> int:
         return int(self.lib.b200_ctx_last_step_launches(self.ctx))
 
@@ -366,3 +381,150 @@ class ModelRunner:
             self.close()
         except Exception:
             pass
+
+
+class StackRunner(ModelRunner):
+    """Device state of a model described layer by layer (config.is_stack_config): same step, sampling and read-back calls as
+    ModelRunner (they are the ctx's), its own construction: per-layer descriptors, per-layer paged caches (head sizes differ
+    by layer), fp32 cos|sin tables shared between layers of equal rotation.  dtype "float32" runs activations, caches and
+    matrix products in true fp32."""
+
+    def __init__(self, cfg, device: Optional[torch.device] = None, *, max_tokens: int = 2048, max_model_len: int = 8192,
+                 block_size: int = 64, n_blocks: Optional[int] = None, kv_cache_gib: Optional[float] = None,
+                 graphs: bool = True, dtype: str = "bfloat16", max_logit_rows: int = 512, tp_rank: int = 0, tp_world: int = 1):
+        if not torch.cuda.is_available():
+            raise RuntimeError("StackRunner needs a CUDA device (B200, sm_100a); there is no CPU path")
+        if tp_world != 1:
+            raise ValueError("layer-list models run on one GPU (tensor_parallel_size 1)")
+        if dtype not in ("bfloat16", "float32"):
+            raise ValueError(f"dtype {dtype!r}: bfloat16 or float32")
+        self.lib = _abi.lib()
+        self.cfg = cfg
+        self.f32 = dtype == "float32"
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        torch.cuda.set_device(self.device)
+        if not self.lib.b200_device_ok():
+            raise RuntimeError("the current CUDA device is not compute capability 10.x (B200)")
+        self.block_size, self.max_tokens, self.max_model_len = block_size, max_tokens, max_model_len
+        self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
+        self.tp_rank, self.tp_world = 0, 1
+        self.vocab_local = cfg.vocab
+        self.stream = torch.cuda.Stream(device=self.device)
+
+        # rotation tables, one per distinct specification
+        self._tables: List[torch.Tensor] = []
+        keys: Dict[tuple, int] = {}
+
+        def table_of(spec) -> int:
+            if spec is None:
+                return -1
+            k = spec.key()
+            if k not in keys:
+                if len(self._tables) >= 16:
+                    raise ValueError("more than 16 distinct rotation tables")
+                keys[k] = len(self._tables)
+                self._tables.append(spec.table(max(max_model_len, 16)).to(self.device))
+            return keys[k]
+
+        layers = (_abi.StackLayer * cfg.n_layers)()
+        for i, L in enumerate(cfg.layers):
+            a, f = L.mixer, L.mlp
+            layers[i] = _abi.StackLayer(
+                mixer=_abi.MIXER_ATTENTION, heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim,
+                rot_dims=a.rot.dims if a.rot else 0, rot_table=table_of(a.rot), vrot_table=table_of(a.value_rot), scale=a.scale,
+                mlp=_abi.MLP_MOE if f else _abi.MLP_NONE, experts=f.experts if f else 0, top=f.top if f else 0,
+                groups=f.groups if f else 0, keep=f.keep if f else 0, ff=f.ff if f else 0)
+        sc = _abi.StackCfg(width=cfg.width, vocab=cfg.vocab, n_layers=cfg.n_layers, embed_scale=cfg.embed_scale,
+                           norm_eps=cfg.norm_eps, f32=int(self.f32), block_size=block_size, max_tokens=max_tokens,
+                           max_blocks_per_seq=self.max_blocks_per_seq, max_logit_rows=min(max_logit_rows, max_tokens))
+        h = C.c_void_p()
+        _abi.check(self.lib.b200_stack_create(C.byref(sc), layers, C.byref(h)))
+        self.ctx = h
+        _abi.check(self.lib.b200_ctx_set_graphs(self.ctx, int(graphs)))
+        for i, t in enumerate(self._tables):
+            _abi.check(self.lib.b200_stack_set_rot_table(self.ctx, i, t.data_ptr(), t.shape[0], t.shape[2]))
+
+        # paged caches, one pair per layer: [n_blocks][kv_heads][block][dim | vdim], zero-filled
+        per_block = cfg.kv_bytes_per_token(self.f32) * block_size
+        if n_blocks is None:
+            if kv_cache_gib is None:
+                free, _ = torch.cuda.mem_get_info(self.device)
+                kv_cache_gib = max(free / 2 ** 30 * 0.5, 0.25)
+            n_blocks = max(int(kv_cache_gib * 2 ** 30) // per_block, 2)
+        self.n_blocks = n_blocks
+        cdt = torch.float32 if self.f32 else torch.bfloat16
+        self.k_cache, self.v_cache = [], []
+        for i, L in enumerate(cfg.layers):
+            a = L.mixer
+            k = torch.zeros((n_blocks, a.kv_heads, block_size, a.dim), dtype=cdt, device=self.device)
+            v = torch.zeros((n_blocks, a.kv_heads, block_size, a.vdim), dtype=cdt, device=self.device)
+            self.k_cache.append(k)
+            self.v_cache.append(v)
+            _abi.check(self.lib.b200_stack_set_kv_cache(self.ctx, i, k.data_ptr(), v.data_ptr(), n_blocks))
+        self._alloc_host_buffers(max_logit_rows)
+        self._tap = None
+
+    def _set(self, layer: int, kind: int, t: torch.Tensor):
+        dt = torch.float32 if kind in _abi.SW_F32 else torch.bfloat16
+        t = t.to(device=self.device, dtype=dt).contiguous()
+        self._weights.append(t)
+        rows, cols = (t.shape[0], t.shape[1]) if t.dim() == 2 else (t.shape[0], 1)
+        _abi.check(self.lib.b200_stack_set_weight(self.ctx, layer, kind, t.data_ptr(), rows, cols))
+
+    def load_weights(self, w: Dict[str, torch.Tensor]):
+        from .weights import STACK_WEIGHT_MAPS
+        for layer, kind, t in STACK_WEIGHT_MAPS[self.cfg.architecture](w, self.cfg):
+            self._set(layer, kind, t)
+
+    def init_random_weights(self, seed: int = 1234, std: float = 0.02):
+        """Random-init weights generated on the device (benchmarks).  Norm weights are 1, the router bias 0."""
+        c, A = self.cfg, _abi
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+
+        def rnd(*shape, sd=std):
+            t = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+            t.normal_(0.0, sd, generator=g)
+            return t
+
+        ones = torch.ones(c.width, dtype=torch.float32, device=self.device)
+        self._set(0, A.SW_EMBED, rnd(c.vocab, c.width, sd=1.0))
+        self._set(0, A.SW_FINAL_NORM, ones)
+        self._set(0, A.SW_HEAD, rnd(c.vocab, c.width))
+        for i, L in enumerate(c.layers):
+            a, f = L.mixer, L.mlp
+            for kind in (A.SW_NORM_MIX_PRE, A.SW_NORM_MIX_POST):
+                self._set(i, kind, ones)
+            self._set(i, A.SW_QKV, rnd(a.heads * a.dim + a.kv_heads * (a.dim + a.vdim), c.width))
+            self._set(i, A.SW_Q_NORM, torch.ones(a.heads * a.dim, device=self.device))
+            self._set(i, A.SW_K_NORM, torch.ones(a.kv_heads * a.dim, device=self.device))
+            self._set(i, A.SW_O, rnd(c.width, a.heads * a.vdim))
+            if f:
+                for kind in (A.SW_NORM_MLP_PRE, A.SW_NORM_MLP_POST):
+                    self._set(i, kind, ones)
+                self._set(i, A.SW_ROUTER, rnd(f.experts, c.width))
+                self._set(i, A.SW_EXPERT_GATE_UP, rnd(f.experts * 2 * f.ff, c.width))
+                self._set(i, A.SW_EXPERT_DOWN, rnd(f.experts * c.width, f.ff))
+
+    def init_tp(self, group=None, peer_allreduce: bool = None):
+        return
+
+    def set_stream_tap(self, on: bool) -> Optional[torch.Tensor]:
+        """Parity tests: after every step, [n_layers][max_tokens rows used][width] fp32 residual streams (graph replay off)."""
+        if on:
+            self._tap = torch.zeros(self.cfg.n_layers * self.max_tokens * self.cfg.width, dtype=torch.float32, device=self.device)
+            _abi.check(self.lib.b200_stack_set_stream_tap(self.ctx, self._tap.data_ptr()))
+        else:
+            _abi.check(self.lib.b200_stack_set_stream_tap(self.ctx, None))
+            self._tap = None
+        return self._tap
+
+
+def make_runner(cfg, **kw):
+    """The runner class follows the configuration class (config.load_model_config picks that by config.json)."""
+    from .config import is_stack_config
+    if is_stack_config(cfg):
+        kw.pop("tp_rank", None), kw.pop("tp_world", None)
+        return StackRunner(cfg, **kw)
+    kw.pop("dtype", None), kw.pop("max_logit_rows", None)
+    return ModelRunner(cfg, **kw)

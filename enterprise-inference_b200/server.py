@@ -72,8 +72,8 @@ def make_arg_parser() -> argparse.ArgumentParser:
 
 
 def validate_args(args) -> None:
-    if args.dtype not in ("bfloat16", "bf16", "auto"):
-        raise SystemExit(f"--dtype {args.dtype}: this backend computes in bfloat16 only")
+    if args.dtype not in ("bfloat16", "bf16", "auto", "float32", "fp32", "float"):
+        raise SystemExit(f"--dtype {args.dtype}: bfloat16, or float32 for models described layer by layer")
     if args.pipeline_parallel_size != 1:
         raise SystemExit("--pipeline-parallel-size > 1 is not supported (the reference never sets it, values.yaml:188)")
     if args.block_size % 64:
@@ -731,12 +731,12 @@ class _RunnerFactory:
         self.args = args
 
     def resolve(self):
-        from .config import from_hf_config, get_config
+        from .config import get_config, load_model_config
         from .weights import resolve_hf_snapshot
         a = self.args
         try:
             path = resolve_hf_snapshot(a.model)
-            return path, from_hf_config(path)
+            return path, load_model_config(path)   # the model class follows config.json
         except FileNotFoundError:
             if not a.random_weights:
                 raise
@@ -744,14 +744,15 @@ class _RunnerFactory:
 
     def __call__(self, rank: int, world: int):
         import torch
-        from .runner import ModelRunner
+        from .runner import make_runner
         from .weights import load_safetensors_dir
         a = self.args
         path, cfg = self.resolve()
         torch.cuda.set_device(rank)
-        runner = ModelRunner(cfg, max_tokens=a.max_num_batched_tokens, max_model_len=a.max_model_len,
+        runner = make_runner(cfg, max_tokens=a.max_num_batched_tokens, max_model_len=a.max_model_len,
                              block_size=a.block_size, kv_cache_gib=a.kv_cache_gib, n_blocks=getattr(a, "n_blocks", None),
-                             tp_rank=rank, tp_world=world, graphs=True)
+                             tp_rank=rank, tp_world=world, graphs=True,
+                             dtype="float32" if a.dtype in ("float32", "fp32", "float") else "bfloat16")
         if a.random_weights or path is None:
             runner.init_random_weights()
         else:

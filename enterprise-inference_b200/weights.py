@@ -88,3 +88,35 @@ def resolve_hf_snapshot(model_id: str, hf_home: str = None) -> str:
     if not snaps:
         raise FileNotFoundError(f"{model_id} is not in the HF cache at {hf_home} (HF_HOME); the server does not download")
     return snaps[-1]
+
+
+def bopilorn_weights(w: Dict[str, torch.Tensor], cfg) -> Iterator[Tuple[int, int, torch.Tensor]]:
+    """(layer, b200_stack_weight kind, tensor) of a Bopilorn checkpoint: `embed`, `head`, `final.norm`, and per layer i
+    `l<i>.norm1|norm1b|norm2|norm2b`, `l<i>.mix.q|k|v|o`, `l<i>.mix.q.norm|k.norm`, `l<i>.mlp.router|correction`,
+    `l<i>.mlp.e<j>.gate|up|down`.  q|k|v are fused row-wise, the experts stacked ([E][2 ff][width] gate rows then up rows,
+    [E][width][ff]); vectors are handed over in fp32."""
+    from . import _abi as A
+    yield 0, A.SW_EMBED, w["embed"]
+    yield 0, A.SW_FINAL_NORM, w["final.norm"]
+    yield 0, A.SW_HEAD, w["head"]
+    for i, L in enumerate(cfg.layers):
+        p = f"l{i}."
+        yield i, A.SW_NORM_MIX_PRE, w[p + "norm1"]
+        yield i, A.SW_NORM_MIX_POST, w[p + "norm1b"]
+        yield i, A.SW_QKV, torch.cat([w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"]], 0)
+        yield i, A.SW_Q_NORM, w[p + "mix.q.norm"]
+        yield i, A.SW_K_NORM, w[p + "mix.k.norm"]
+        yield i, A.SW_O, w[p + "mix.o"]
+        if L.mlp is None:
+            continue
+        yield i, A.SW_NORM_MLP_PRE, w[p + "norm2"]
+        yield i, A.SW_NORM_MLP_POST, w[p + "norm2b"]
+        yield i, A.SW_ROUTER, w[p + "mlp.router"]
+        if p + "mlp.correction" in w:
+            yield i, A.SW_ROUTER_BIAS, w[p + "mlp.correction"]
+        E = L.mlp.experts
+        yield i, A.SW_EXPERT_GATE_UP, torch.cat([torch.cat([w[f"{p}mlp.e{e}.gate"], w[f"{p}mlp.e{e}.up"]], 0) for e in range(E)], 0)
+        yield i, A.SW_EXPERT_DOWN, torch.cat([w[f"{p}mlp.e{e}.down"] for e in range(E)], 0)
+
+
+STACK_WEIGHT_MAPS = {"Bopilorn": bopilorn_weights}

@@ -350,6 +350,79 @@ B200_API int b200_allreduce_bf16(b200_ctx* ctx, void* buf, int64_t count, void* 
 B200_API int b200_tp_allreduce(b200_ctx* ctx, int32_t buf_idx, const void* partial, int32_t n_tokens, void* res,
                       const void* norm_w, void* y, void* stream);
 
+/* ---- models described layer by layer ---------------------------------------------------------------------------------
+ * No counterpart in the reference chart's model list: decoder-only designs whose layers differ from one another or use
+ * mechanisms outside the Llama / Qwen2 stack are given as a list of layer descriptors.  The ctx they create is driven by
+ * the SAME step, sampling, log-probability and logit-adjust entry points as above (b200_decode_step[_host],
+ * b200_ctx_sample_last, ...); only construction, weights and caches differ.  Single GPU (tp_world 1).
+ *
+ * Layer = mixer sublayer + optional feed-forward sublayer over an fp32 residual stream x, each sublayer wrapped in bias-free
+ * layer norms on both sides:  x += norm_post(sublayer(norm_pre(x))).
+ *
+ * B200_MIXER_ATTENTION: grouped-query causal softmax attention.  q and k are RMS-normalised over the WHOLE projection
+ * (weights of that size) before rotation; the leading rot_dims dimensions of each q/k head rotate in the interleaved pair
+ * layout by angles read from cos|sin table `rot_table` (frequency scaling and magnitude factors are baked into the table by
+ * the host); values are scaled to unit RMS per head and, when vrot_table >= 0, rotated over all their dimensions by their
+ * own position, with the attention output turned back by the query's position; score = q.k * scale.
+ *
+ * B200_MLP_MOE: routed experts.  Router softmax over all experts; choice by score + bias, group-limited (experts in
+ * `groups` equal runs of neighbours, only the `keep` best groups eligible), `top` experts; mixing weights = the plain
+ * softmax scores, not renormalised; expert = down(silu(gate x) * (up x)). */
+typedef enum b200_mixer_kind { B200_MIXER_ATTENTION = 1 } b200_mixer_kind;
+typedef enum b200_mlp_kind { B200_MLP_NONE = 0, B200_MLP_MOE = 1 } b200_mlp_kind;
+
+typedef struct b200_stack_layer {
+  int32_t mixer;                       /* b200_mixer_kind */
+  int32_t heads, kv_heads, dim, vdim;  /* query heads, key/value heads, q/k head size, value head size */
+  int32_t rot_dims;                    /* rotated leading dimensions of each q/k head (even; 0: none) */
+  int32_t rot_table, vrot_table;       /* table indices (b200_stack_set_rot_table); -1: no rotation */
+  float scale;                         /* score scale */
+  int32_t mlp;                         /* b200_mlp_kind */
+  int32_t experts, top, groups, keep, ff;
+} b200_stack_layer;
+
+typedef struct b200_stack_cfg {
+  int32_t width, vocab, n_layers;
+  float embed_scale;                   /* x = table[id] * embed_scale */
+  float norm_eps;
+  int32_t f32;                         /* 0: bf16 activations, cache and matrix products (fp32 accumulation; residual stream,
+                                          norms, rotations, scores, softmax and routers in fp32); 1: everything in true fp32 */
+  int32_t block_size, max_tokens, max_blocks_per_seq, max_logit_rows;
+} b200_stack_cfg;
+
+typedef enum b200_stack_weight {
+  B200_SW_EMBED = 0,        /* bf16 [vocab][width] */
+  B200_SW_FINAL_NORM = 1,   /* f32  [width] */
+  B200_SW_HEAD = 2,         /* bf16 [vocab][width] */
+  B200_SW_NORM_MIX_PRE = 3, /* f32  [width]  the four layer norms of a layer */
+  B200_SW_NORM_MIX_POST = 4,
+  B200_SW_NORM_MLP_PRE = 5,
+  B200_SW_NORM_MLP_POST = 6,
+  B200_SW_QKV = 7,          /* bf16 [heads*dim + kv_heads*dim + kv_heads*vdim][width]: q rows, k rows, v rows */
+  B200_SW_Q_NORM = 8,       /* f32  [heads*dim] */
+  B200_SW_K_NORM = 9,       /* f32  [kv_heads*dim] */
+  B200_SW_O = 10,           /* bf16 [width][heads*vdim] */
+  B200_SW_ROUTER = 11,      /* bf16 [experts][width] */
+  B200_SW_ROUTER_BIAS = 12, /* f32  [experts]  added to the scores for the choice only (may stay unset: zeros) */
+  B200_SW_EXPERT_GATE_UP = 13, /* bf16 [experts][2*ff][width]: per expert the gate rows, then the up rows */
+  B200_SW_EXPERT_DOWN = 14  /* bf16 [experts][width][ff] */
+} b200_stack_weight;
+
+B200_API int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_layer* layers, b200_ctx** out);
+/* Pointers are borrowed for the life of the ctx; rows/cols are checked ([rows][cols], vectors as [n][1]). */
+B200_API int b200_stack_set_weight(b200_ctx* ctx, int32_t layer, int32_t kind, const void* w, int64_t rows, int64_t cols);
+/* Paged cache of one layer, caller-owned: k [n_blocks][kv_heads][block_size][dim], v [...][vdim]; bf16, or fp32 when the
+ * ctx was created with f32.  Every layer gets the same n_blocks (one block table serves all layers). */
+B200_API int b200_stack_set_kv_cache(b200_ctx* ctx, int32_t layer, void* k_cache, void* v_cache, int64_t n_blocks);
+/* cos|sin table `index` (0..15): fp32 [n_pos][2][half] (the cos row of a position, then its sin row). */
+B200_API int b200_stack_set_rot_table(b200_ctx* ctx, int32_t index, const float* table, int64_t n_pos, int32_t half);
+/* After every layer of a step, the residual stream is copied to out[layer][n_tokens][width] fp32 (NULL: off; turns graph
+ * replay off while set).  Parity tests. */
+B200_API int b200_stack_set_stream_tap(b200_ctx* ctx, float* out);
+/* The logit rows of the LAST step as fp32 [n_rows][vocab] into host memory (asynchronously: synchronise the stream before
+ * reading).  With f32 they are the unrounded logits; otherwise the bf16 logits widened.  Works for every ctx on one GPU. */
+B200_API int b200_ctx_logits_last_f32(b200_ctx* ctx, int32_t n_rows, float* host_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
