@@ -102,6 +102,16 @@ SIGNATURES = {
     "b200_stack_set_rot_table": (C.c_int, [_vp, _i32, _vp, _i64, _i32]),
     "b200_stack_set_stream_tap": (C.c_int, [_vp, _vp]),
     "b200_ctx_logits_last_f32": (C.c_int, [_vp, _i32, _vp, _vp]),
+    "b200_layernorm_stream": (C.c_int, [_i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]),
+    "b200_qk_norm_rotate_cache": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
+                                            _i32, _i32, _f32, _i64, _vp]),
+    "b200_paged_attn_anydim_workspace_bytes": (_i64, [_i32]),
+    "b200_paged_attn_anydim": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _i32,
+                                         _i32, _f32, _i32, _vp, _vp]),
+    "b200_moe_route": (C.c_int, [_i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "b200_moe_workspace_bytes": (_i64, [_i32, _i32, _i32]),
+    "b200_moe_experts": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "b200_linear_simt": (C.c_int, [_i32, _i32, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
 }
 
 _lib = None

@@ -228,10 +228,15 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
           m[k] = mn;
           const int nn = min(n, ctx - base);
           float* op = Os + qi * vdim;
-          for (int d = lane; d < vdim; d += 32) {
-            float a = op[d] * corr;
-            for (int jj = 0; jj < nn; ++jj) a = fmaf(__shfl_sync(0xffffffffu, p, jj), Vs[jj * vst + d], a);
-            op[d] = a;
+          for (int d0 = 0; d0 < vdim; d0 += 32) {   // the whole warp walks every slice: the shuffles need all lanes
+            const int d = d0 + lane;
+            const bool live = d < vdim;
+            float a = live ? op[d] * corr : 0.f;
+            for (int jj = 0; jj < nn; ++jj) {
+              const float pj = __shfl_sync(0xffffffffu, p, jj);
+              if (live) a = fmaf(pj, Vs[jj * vst + d], a);
+            }
+            if (live) op[d] = a;
           }
         }
       }

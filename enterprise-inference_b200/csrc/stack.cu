@@ -390,3 +390,60 @@ extern "C" int b200_ctx_logits_last_f32(b200_ctx* c, int32_t n_rows, float* host
   }
   return B200_OK;
 }
+
+// ---- per-kernel entry points ---------------------------------------------------------------------------------------------
+extern "C" int b200_layernorm_stream(int32_t f32, float* x, const void* y, const float* yparts, int32_t n_parts, const float* w_post,
+                                     const float* w_next, void* out, const int32_t* rows, int32_t T, int32_t width, float eps,
+                                     void* stream) {
+  B200_REQUIRE(x && T >= 0 && width > 0, B200_ERR_INVALID, "layernorm_stream: bad argument");
+  return layernorm_stream(f32 != 0, x, y, yparts, n_parts, w_post, w_next, out, rows, T, width, eps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_qk_norm_rotate_cache(int32_t f32, const void* qkv, const float* qw, const float* kw, const int32_t* positions,
+                                         const int32_t* slots, const float* rot, int32_t rot_dims, const float* vrot, float* q_out,
+                                         void* kc, void* vc, int32_t T, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                                         int32_t block_size, float eps, int64_t max_pos, void* stream) {
+  B200_REQUIRE(qkv && qw && kw && positions && slots && q_out && kc && vc && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 &&
+                   block_size > 0 && max_pos > 0,
+               B200_ERR_INVALID, "qk_norm_rotate_cache: bad argument");
+  return qk_norm_rotate_cache(f32 != 0, qkv, qw, kw, positions, slots, rot, rot ? rot_dims : 0, vrot, q_out, kc, vc, T, heads, kv_heads,
+                              dim, vdim, block_size, eps, max_pos, (cudaStream_t)stream);
+}
+
+extern "C" int64_t b200_paged_attn_anydim_workspace_bytes(int32_t T) { return paged_attn_anydim_workspace_bytes(T); }
+
+extern "C" int b200_paged_attn_anydim(int32_t f32, const float* q, const void* kc, const void* vc, const int32_t* block_table,
+                                      int32_t bt_stride, const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions,
+                                      const float* vrot, int64_t max_pos, void* out, int32_t T, int32_t heads, int32_t kv_heads,
+                                      int32_t dim, int32_t vdim, int32_t block_size, float scale, int32_t shared_tiles, void* ws,
+                                      void* stream) {
+  B200_REQUIRE(q && kc && vc && block_table && ctx_lens && positions && out && block_size > 0, B200_ERR_INVALID,
+               "paged_attn_anydim: bad argument");
+  B200_REQUIRE(!shared_tiles || ws, B200_ERR_INVALID, "paged_attn_anydim: the shared-tile form needs its workspace");
+  return paged_attn_anydim(f32 != 0, q, kc, vc, block_table, bt_stride, row_to_seq, ctx_lens, positions, vrot, max_pos, out, T, heads,
+                           kv_heads, dim, vdim, block_size, scale, shared_tiles ? 1 : 0, ws, (cudaStream_t)stream);
+}
+
+extern "C" int b200_moe_route(int32_t f32, const void* x, const void* w_router, const float* bias, int32_t T, int32_t width,
+                              int32_t experts, int32_t top, int32_t groups, int32_t keep, int32_t* out_ids, float* out_w, void* stream) {
+  B200_REQUIRE(x && w_router && out_ids && out_w && width > 0, B200_ERR_INVALID, "moe_route: bad argument");
+  return moe_route(f32 != 0, x, (const __nv_bfloat16*)w_router, bias, T, width, experts, top, groups, keep, out_ids, out_w,
+                   (cudaStream_t)stream);
+}
+
+extern "C" int64_t b200_moe_workspace_bytes(int32_t T, int32_t top, int32_t experts) { return moe_workspace_bytes(T, top, experts); }
+
+extern "C" int b200_moe_experts(int32_t f32, const void* x, const void* w_gu, const void* w_down, const int32_t* ids, const float* wts,
+                                int32_t T, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts, void* ws,
+                                void* stream) {
+  B200_REQUIRE(x && w_gu && w_down && ids && wts && parts && width > 0 && ff > 0 && experts > 0 && top > 0, B200_ERR_INVALID,
+               "moe_experts: bad argument");
+  return moe_experts(f32 != 0, x, (const __nv_bfloat16*)w_gu, (const __nv_bfloat16*)w_down, ids, wts, T, width, ff, experts, top,
+                     parts, ws, (cudaStream_t)stream);
+}
+
+extern "C" int b200_linear_simt(int32_t x_f32, int32_t y_f32, const void* x, int64_t ldx, const void* w, void* y, int64_t ldy,
+                                int32_t T, int32_t n_out, int32_t k, void* stream) {
+  B200_REQUIRE(x && w && y && T >= 0 && n_out > 0 && k > 0, B200_ERR_INVALID, "linear_simt: bad argument");
+  return linear_simt(x_f32 != 0, y_f32 != 0, x, ldx, (const __nv_bfloat16*)w, y, ldy, T, n_out, k, (cudaStream_t)stream);
+}

@@ -423,6 +423,42 @@ B200_API int b200_stack_set_stream_tap(b200_ctx* ctx, float* out);
  * reading).  With f32 they are the unrounded logits; otherwise the bf16 logits widened.  Works for every ctx on one GPU. */
 B200_API int b200_ctx_logits_last_f32(b200_ctx* ctx, int32_t n_rows, float* host_out, void* stream);
 
+/* Per-kernel entry points of the mechanisms above (unit tests, profiling).  f32 selects the element type of activations
+ * and caches (0: bf16, 1: fp32); vectors of norm weights, tables, queries and partial rows are always fp32. */
+/* x (fp32 stream [T][width]) += LN(y) * w_post, where y is an activation row [T][width] or, when y is NULL, the sum over
+ * n_parts fp32 partial rows yparts[T][n_parts][width] (both NULL: x is left alone); then, when w_next is given,
+ * out[t] = LN(x[rows ? rows[t] : t]) * w_next.  LN: (v - mean) / sqrt(mean((v - mean)^2) + eps). */
+B200_API int b200_layernorm_stream(int32_t f32, float* x, const void* y, const float* yparts, int32_t n_parts, const float* w_post,
+                          const float* w_next, void* out, const int32_t* rows, int32_t n_tokens, int32_t width, float eps,
+                          void* stream);
+/* qkv [T][heads*dim + kv_heads*dim + kv_heads*vdim] -> q_out fp32 [T][heads*dim]; k, v into the paged caches at
+ * slot_mapping[t].  rot / vrot: cos|sin tables [max_pos][2][rot_dims/2] / [max_pos][2][vdim/2] (NULL: no rotation). */
+B200_API int b200_qk_norm_rotate_cache(int32_t f32, const void* qkv, const float* q_norm_w, const float* k_norm_w,
+                              const int32_t* positions, const int32_t* slot_mapping, const float* rot, int32_t rot_dims,
+                              const float* vrot, float* q_out, void* k_cache, void* v_cache, int32_t n_tokens, int32_t heads,
+                              int32_t kv_heads, int32_t dim, int32_t vdim, int32_t block_size, float eps, int64_t max_pos,
+                              void* stream);
+/* Causal paged attention of fp32 queries [T][heads*dim] over caches [block][kv_heads][block_size][dim | vdim]; out
+ * [T][heads*vdim].  vrot != NULL: the output of row t is rotated by -positions[t].  shared_tiles 0: one CTA per (row, head);
+ * 1: runs of consecutive rows of a sequence share K/V tiles (workspace: b200_paged_attn_anydim_workspace_bytes(T)). */
+B200_API int64_t b200_paged_attn_anydim_workspace_bytes(int32_t n_tokens);
+B200_API int b200_paged_attn_anydim(int32_t f32, const float* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                           int32_t bt_stride, const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions,
+                           const float* vrot, int64_t max_pos, void* out, int32_t n_tokens, int32_t heads, int32_t kv_heads,
+                           int32_t dim, int32_t vdim, int32_t block_size, float scale, int32_t shared_tiles, void* workspace,
+                           void* stream);
+/* Router: out_ids / out_weights [T][top].  bias may be NULL. */
+B200_API int b200_moe_route(int32_t f32, const void* x, const void* w_router, const float* bias, int32_t n_tokens, int32_t width,
+                   int32_t experts, int32_t top, int32_t groups, int32_t keep, int32_t* out_ids, float* out_weights, void* stream);
+/* Chosen experts: parts [T][top][width] fp32, each row already times its weight.  workspace: b200_moe_workspace_bytes. */
+B200_API int64_t b200_moe_workspace_bytes(int32_t n_tokens, int32_t top, int32_t experts);
+B200_API int b200_moe_experts(int32_t f32, const void* x, const void* w_gate_up, const void* w_down, const int32_t* ids,
+                     const float* weights, int32_t n_tokens, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts,
+                     void* workspace, void* stream);
+/* y[T][n_out] = x[T][k] . w[n_out][k]^T on CUDA cores in true fp32; w bf16, x / y fp32 or bf16. */
+B200_API int b200_linear_simt(int32_t x_f32, int32_t y_f32, const void* x, int64_t ldx, const void* w, void* y, int64_t ldy,
+                     int32_t n_tokens, int32_t n_out, int32_t k, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
