@@ -612,6 +612,103 @@ def run_b200(args):
         env.dist.destroy_process_group()
 
 
+
+# ---- --design: a layer-list design beside the closest fixed-stack model at equal size ----------------------------------------
+DESIGN_SIZES = {
+    # layer shapes in the range of real models of that kind (random weights, a few layers): width, heads, kv heads, head size,
+    # experts / chosen / expert width; the Llama arm gets the same width, heads and layers and intermediate = chosen x expert width
+    "w2048-e32": dict(width=2048, heads=16, kv=4, dim=128, layers=4, experts=32, top=4, ff=1024, vocab=32768, groups=4, keep=2),
+    "w4096-e64": dict(width=4096, heads=32, kv=8, dim=128, layers=2, experts=64, top=8, ff=512, vocab=32768, groups=8, keep=4),
+    "w1024-d64": dict(width=1024, heads=16, kv=2, dim=64, layers=4, experts=16, top=2, ff=1024, vocab=32768, groups=1, keep=1),
+}
+
+
+def _design_batch(R, n_seqs, ctx, n_new, bs, vocab):
+    """n_seqs sequences that already hold ctx tokens and bring n_new rows each; the last row of each is a logit row."""
+    import numpy as np
+    per = (ctx + n_new + bs - 1) // bs
+    b = R.StepBatch()
+    rng = np.random.default_rng(0)
+    for s in range(n_seqs):
+        table = list(range(s * per, (s + 1) * per))
+        for p in range(ctx, ctx + n_new):
+            b.ids.append(int(rng.integers(0, vocab)))
+            b.positions.append(p)
+            b.slots.append(table[p // bs] * bs + p % bs)
+            b.ctx_lens.append(p + 1)
+            b.row_to_seq.append(s)
+        b.logit_rows.append(len(b.ids) - 1)
+        b.block_tables.append(table)
+    return b, n_seqs * per
+
+
+def _time_steps(torch, r, batch, K, W, flush):
+    for _ in range(W):
+        r.step(batch)
+    ts = []
+    for _ in range(K):
+        flush.add_(1.0)                      # 512 MiB written: L2 holds nothing of the last step
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(r.stream)
+        r.step(batch, sync=False)
+        e1.record(r.stream)
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def run_design(args):
+    """Prefill and decode throughput of the Bopilorn design beside the Llama stack at equal size (CUDA events on the step's
+    stream, median of K steps after W warm-up steps, L2 flushed between steps; the step includes the H2D copy of its metadata
+    and the D2H copy of its tokens).  One JSON line; the default workload's line and contract are untouched."""
+    import torch
+    Cf, R = importlib.import_module(PKG + ".config"), importlib.import_module(PKG + ".runner")
+    torch.cuda.set_device(0)
+    K, W = min(args.steps, 20), max(args.warmup, 3)
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device="cuda")
+    sampler = ClockSampler(0)
+    sampler.start()
+    t0 = time.monotonic()
+    out = []
+    names = [n for n in DESIGN_SIZES if args.design_size in ("all", n)]
+    for name in names:
+        z = DESIGN_SIZES[name]
+        rot = Cf.RotarySpec(base=50000.0, dims=z["dim"], factor=8.0, original=4096, fast=32.0, slow=1.0, scaled=True)
+        att = Cf.AttentionSpec(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, rot=rot,
+                               value_rot=Cf.RotarySpec(base=50000.0, dims=z["dim"]))
+        moe = Cf.MoESpec(experts=z["experts"], top=z["top"], ff=z["ff"], groups=z["groups"], keep=z["keep"])
+        arms = {"bopilorn": Cf.BopilornConfig(name=name, width=z["width"], vocab=z["vocab"], embed_scale=1.0,
+                                              layers=[Cf.StackLayerSpec(mixer=att, mlp=moe) for _ in range(z["layers"])])}
+        if z["dim"] == 128:
+            arms["llama"] = Cf.ModelConfig(name=name, hidden=z["width"], n_layers=z["layers"], n_q_heads=z["heads"], n_kv_heads=z["kv"],
+                                           intermediate=z["top"] * z["ff"], vocab=z["vocab"], max_pos=8192)
+        rec = {"size": name, "shape": z, "ms": {}, "tok_s": {}}
+        for arm, cfg in arms.items():
+            bs = 128
+            cases = {"prefill_2048": (1, 0, 2048), "decode_b64_ctx512": (64, 512, 1), "decode_b1_ctx512": (1, 512, 1)}
+            n_blocks = 64 * 5 + 8
+            r = R.make_runner(cfg, max_tokens=2048, max_model_len=4096, block_size=bs, n_blocks=n_blocks)
+            r.init_random_weights(seed=7)
+            rec["ms"][arm], rec["tok_s"][arm] = {}, {}
+            for case, (n_seqs, ctx, n_new) in cases.items():
+                batch, _ = _design_batch(R, n_seqs, ctx, n_new, bs, z["vocab"])
+                ms = _time_steps(torch, r, batch, K, W, flush)
+                rec["ms"][arm][case] = round(ms, 4)
+                rec["tok_s"][arm][case] = round(n_seqs * n_new / ms * 1e3, 1)
+            rec.setdefault("launches_per_step", {})[arm] = r.last_step_launches()
+            rec.setdefault("weight_gb", {})[arm] = round(cfg.weight_bytes() / 1e9, 3)
+            r.close()
+            del r
+            gc.collect()
+            torch.cuda.empty_cache()
+        out.append(rec)
+    clocks = sampler.stop(t0, time.monotonic())
+    emit({"metric": "design_compare", "design": "Bopilorn", "closest": "llama (fixed decoder stack)", "dtype": "bf16",
+          "data": "synthetic, random-init weights", "steps": K, "warmup": W, "l2": "flushed between steps (512 MiB written)",
+          "sizes": out, "clocks": clocks})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -621,9 +718,15 @@ def main():
     ap.add_argument("--workload", default="llama8b-bs64", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true", help="skip the `also` and `tp` sections of the default run")
+    ap.add_argument("--design", default=None, choices=["bopilorn"],
+                    help="instead of the default workload: prefill / decode throughput of this design beside the closest fixed-stack "
+                         "model at equal size")
+    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(DESIGN_SIZES))
     args = ap.parse_args()
     claim_stdout()
-    if args.impl == "reference":
+    if args.design:
+        run_design(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         args.warmup = max(args.warmup, 3)
