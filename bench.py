@@ -674,9 +674,9 @@ def run_design(args):
     names = [n for n in DESIGN_SIZES if args.design_size in ("all", n)]
     for name in names:
         z = DESIGN_SIZES[name]
-        rot = Cf.RotarySpec(base=50000.0, dims=z["dim"], factor=8.0, original=4096, fast=32.0, slow=1.0, scaled=True)
+        rot = Cf.RotarySpec(base=10000.0, dims=z["dim"], factor=4.0, original=4096, fast=32.0, slow=1.0, scaled=True)
         att = Cf.AttentionSpec(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, rot=rot,
-                               value_rot=Cf.RotarySpec(base=50000.0, dims=z["dim"]))
+                               value_rot=Cf.RotarySpec(base=10000.0, dims=z["dim"]))
         moe = Cf.MoESpec(experts=z["experts"], top=z["top"], ff=z["ff"], groups=z["groups"], keep=z["keep"])
         arms = {"bopilorn": Cf.BopilornConfig(name=name, width=z["width"], vocab=z["vocab"], embed_scale=1.0,
                                               layers=[Cf.StackLayerSpec(mixer=att, mlp=moe) for _ in range(z["layers"])])}

@@ -195,6 +195,11 @@ struct LinearExtra {
 int linear_tc(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, const __nv_bfloat16* bias,
               __nv_bfloat16* y, int64_t ldy, int T, int n_out, int k, void* ws, int64_t ws_bytes,
               const LinearExtra* ex, cudaStream_t s);
+// grouped form (gemm_tc.cu): one launch over the gathered token rows of every expert
+int linear_tc_grouped_tile(int pairs, int experts);
+int linear_tc_grouped(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, const __nv_bfloat16* w, int experts, int n_out, int k,
+                      const int32_t* tile_expert, __nv_bfloat16* y, int64_t ldy, const int32_t* row_pair, const float* wts,
+                      float* out, cudaStream_t s);
 int rmsnorm(const __nv_bfloat16* x, __nv_bfloat16* res, const __nv_bfloat16* w, __nv_bfloat16* y, int T,
             int hidden, float eps, cudaStream_t s);
 // fp32 residual stream (RMSNorm folded into the linears): embedding rows -> sres/ssq; stream rows -> normed bf16
@@ -264,7 +269,11 @@ int layernorm_stream(bool f32, float* x, const void* y, const float* yparts, int
 int qk_norm_rotate_cache(bool f32, const void* qkv, const float* qw, const float* kw, const int32_t* positions,
                          const int32_t* slots, const float* rot, int rot_dims, const float* vrot, float* qout, void* kc,
                          void* vc, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float eps,
-                         int64_t max_pos, cudaStream_t s);
+                         int64_t max_pos, cudaStream_t s, __nv_bfloat16* qout16 = nullptr);
+// attention output rows turned back by their position (bf16, in place): the closing step of rotated values when the
+// attention kernel itself does not do it
+int rotate_back_rows(__nv_bfloat16* a, const int32_t* positions, const float* vrot, int T, int heads, int vdim, int64_t max_pos,
+                     cudaStream_t s);
 int convert_f32_to_bf16(const float* in, __nv_bfloat16* out, int64_t n, cudaStream_t s);
 int convert_bf16_to_f32(const __nv_bfloat16* in, float* out, int64_t n, cudaStream_t s);
 // paged softmax attention for any head sizes (attn_anydim.cu)
@@ -274,7 +283,8 @@ int paged_attn_anydim(bool f32, const float* q, const void* kc, const void* vc, 
                       int64_t max_pos, void* out, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float scale,
                       int plan, void* ws, cudaStream_t s);
 // mixture of experts (moe.cu)
-int64_t moe_workspace_bytes(int T, int top, int experts);
+int64_t moe_workspace_bytes(int T, int top, int experts, int width, int ff);
+bool moe_tc_supported(int width, int ff);
 int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
               int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s);
 int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,

@@ -408,8 +408,8 @@ __global__ void __launch_bounds__(256)
 qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict__ qw, const float* __restrict__ kw,
                             const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
                             const float* __restrict__ rot, int rot_dims, const float* __restrict__ vrot,
-                            float* __restrict__ qout, CT* kc, CT* vc, int heads, int kv_heads, int dim, int vdim,
-                            int block_size, float eps, int64_t max_pos) {
+                            float* __restrict__ qout, __nv_bfloat16* __restrict__ qout16, CT* kc, CT* vc, int heads, int kv_heads,
+                            int dim, int vdim, int block_size, float eps, int64_t max_pos) {
   extern __shared__ float row[];
   __shared__ float red[8];
   pdl_wait();
@@ -460,7 +460,8 @@ qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict_
       v = (d & 1) ? fmaf(v, cs, o * sn) : fmaf(v, cs, -o * sn);
     }
     if (is_q) {
-      qout[(int64_t)t * qn + e] = v;
+      if (qout16) qout16[(int64_t)t * qn + e] = __float2bfloat16_rn(v);   // for the tensor-core attention kernels
+      else qout[(int64_t)t * qn + e] = v;
     } else if (slot >= 0) {
       const int g = e / dim;
       if (sizeof(CT) == 4) reinterpret_cast<float*>(kc)[((blk * kv_heads + g) * block_size + off) * dim + d] = v;
@@ -479,6 +480,26 @@ qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict_
     }
     if (sizeof(CT) == 4) reinterpret_cast<float*>(vc)[((blk * kv_heads + g) * block_size + off) * vdim + d] = v;
     else reinterpret_cast<__nv_bfloat16*>(vc)[((blk * kv_heads + g) * block_size + off) * vdim + d] = __float2bfloat16_rn(v);
+  }
+}
+
+// Turns the rows of an attention output back by the query's position: pair (2m, 2m+1) of every head by -pos * f_m, from the
+// table the cache writer used ([pos][cos half | sin half] fp32).  In place, bf16, one thread per pair.
+__global__ void __launch_bounds__(256)
+rotate_back_rows_kernel(__nv_bfloat16* __restrict__ a, const int32_t* __restrict__ positions, const float* __restrict__ vrot,
+                        int heads, int vdim, int64_t max_pos) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, vhalf = vdim >> 1;
+  int pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? (int)max_pos - 1 : pos);
+  const float* cs = vrot + (int64_t)pos * 2 * vhalf;
+  __nv_bfloat162* row = reinterpret_cast<__nv_bfloat162*>(a + (int64_t)t * heads * vdim);
+  for (int i = threadIdx.x; i < heads * vhalf; i += 256) {
+    const int m = i % vhalf;
+    const float2 uv = __bfloat1622float2(row[i]);
+    const float c = cs[m], sn = cs[vhalf + m];
+    row[i] = __floats2bfloat162_rn(fmaf(uv.x, c, uv.y * sn), fmaf(uv.y, c, -uv.x * sn));
   }
 }
 
@@ -574,8 +595,9 @@ int layernorm_stream(bool f32, float* x, const void* y, const float* yparts, int
 int qk_norm_rotate_cache(bool f32, const void* qkv, const float* qw, const float* kw, const int32_t* positions,
                          const int32_t* slots, const float* rot, int rot_dims, const float* vrot, float* qout, void* kc,
                          void* vc, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float eps,
-                         int64_t max_pos, cudaStream_t s) {
+                         int64_t max_pos, cudaStream_t s, __nv_bfloat16* qout16) {
   if (T == 0) return B200_OK;
+  B200_REQUIRE(!(f32 && qout16), B200_ERR_INVALID, "rotation: bf16 queries are for the bf16 mode");
   B200_REQUIRE(dim % 2 == 0 && rot_dims % 2 == 0 && rot_dims <= dim && (vrot == nullptr || vdim % 2 == 0), B200_ERR_UNSUPPORTED,
                "rotation: head sizes must be even (dim %d, rot_dims %d, vdim %d)", dim, rot_dims, vdim);
   const size_t smem = ((size_t)heads * dim + (size_t)kv_heads * (dim + vdim) + kv_heads) * 4;
@@ -584,14 +606,22 @@ int qk_norm_rotate_cache(bool f32, const void* qkv, const float* qw, const float
   if (f32) {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(qk_norm_rotate_cache_kernel<float, float>, 200 * 1024, done[0]));
     B200_CUDA(launch(qk_norm_rotate_cache_kernel<float, float>, dim3(T), dim3(256), smem, s, (const float*)qkv, qw, kw, positions,
-                     slots, rot, rot_dims, vrot, qout, (float*)kc, (float*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos));
+                     slots, rot, rot_dims, vrot, qout, (__nv_bfloat16*)nullptr, (float*)kc, (float*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos));
   } else {
     if (smem > 48 * 1024)
       B200_CUDA(ensure_dynamic_smem(qk_norm_rotate_cache_kernel<__nv_bfloat16, __nv_bfloat16>, 200 * 1024, done[1]));
     B200_CUDA(launch(qk_norm_rotate_cache_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), smem, s,
-                     (const __nv_bfloat16*)qkv, qw, kw, positions, slots, rot, rot_dims, vrot, qout, (__nv_bfloat16*)kc,
+                     (const __nv_bfloat16*)qkv, qw, kw, positions, slots, rot, rot_dims, vrot, qout, qout16, (__nv_bfloat16*)kc,
                      (__nv_bfloat16*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos));
   }
+  return B200_OK;
+}
+
+int rotate_back_rows(__nv_bfloat16* a, const int32_t* positions, const float* vrot, int T, int heads, int vdim, int64_t max_pos,
+                     cudaStream_t s) {
+  B200_REQUIRE(vdim % 2 == 0 && reinterpret_cast<uintptr_t>(a) % 4 == 0, B200_ERR_UNSUPPORTED, "rotate_back: vdim %d must be even", vdim);
+  if (T == 0) return B200_OK;
+  B200_CUDA(launch(rotate_back_rows_kernel, dim3(T), dim3(256), (size_t)0, s, a, positions, vrot, heads, vdim, max_pos));
   return B200_OK;
 }
 

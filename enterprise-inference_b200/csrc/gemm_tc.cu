@@ -23,6 +23,7 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -179,6 +180,15 @@ struct TcParams {
   const int32_t* rows;   // consumer: token t of the launch reads stream row rows[t] (lm_head's logit rows), or null
   int nslab;             // hidden / 128
   float eps;
+  // Grouped form (routed experts): w holds [experts][n_out][k]; token tile j multiplies the rows of expert grp_tile[j]
+  // (-1: the tile is not in use and its CTAs leave at once).  The token rows are the experts' tokens, gathered so that
+  // no tile holds rows of two experts.
+  const int32_t* grp_tile;
+  // kScatter: row t of the launch goes to grp_out[grp_pair[t]][n_out] (fp32, unrounded) times grp_wt[grp_pair[t]];
+  // grp_pair[t] < 0 marks a padding row
+  const int32_t* grp_pair;
+  const float* grp_wt;
+  float* grp_out;
 };
 
 __device__ __forceinline__ void tc_trace(const TcParams& p, int slot) {
@@ -201,7 +211,8 @@ __device__ __forceinline__ void tc_trace(const TcParams& p, int slot) {
 //  kRopeKv   the slab is one head of the fused qkv projection: NeoX RoPE in bf16 arithmetic (R3) on q
 //            and k heads, q rows to y, k/v rows straight into the paged cache at slots[t]
 //  kResidual the linear's output is added to the fp32 residual stream (see TcParams::sres): no y is written
-enum { kPlain = 0, kSiluMul = 1, kRopeKv = 2, kResidual = 3 };
+//  kScatter  (grouped form) the fp32 row times a per-row weight goes to the row the indirection names; no y
+enum { kPlain = 0, kSiluMul = 1, kRopeKv = 2, kResidual = 3, kScatter = 4 };
 
 
 // One thread finalises 4 consecutive slab rows (r4..r4+3, lane = r4/4) of one token.
@@ -253,6 +264,20 @@ __device__ __forceinline__ void finalize4(const TcParams& p, int m_tile, int lan
     ss = fmaf(sn.w, sn.w, ss);
     ss = warp_sum(ss);
     if (lane == 0) p.ssq[(int64_t)tok * p.nslab + m_tile] = ss;
+  } else if (MODE == kScatter) {
+    const int pair = __ldg(p.grp_pair + tok);   // warp-uniform
+    if (pair < 0) return;
+    const float wt = __ldg(p.grp_wt + pair);
+    const int row = m_tile * kBlockM + r4;
+    float* dst = p.grp_out + (int64_t)pair * p.n_out + row;
+    if (row + 3 < p.n_out && (p.n_out % 4 == 0)) {
+      *reinterpret_cast<float4*>(dst) = make_float4(a.x * wt, a.y * wt, a.z * wt, a.w * wt);
+    } else {
+      const float o[4] = {a.x * wt, a.y * wt, a.z * wt, a.w * wt};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (row + e < p.n_out) dst[e] = o[e];
+    }
   } else {  // kRopeKv
     const int head = m_tile;
     float o[4];
@@ -406,6 +431,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int base = p.n_kblocks / p.splits, rem = p.n_kblocks % p.splits;
   const int kb0 = split * base + min(split, rem);
   const int nkb = base + (split < rem ? 1 : 0);
+  // grouped form: the expert of this token tile picks the weight rows; the table is written by the kernel before this one
+  int w_row0 = m_tile * kBlockM;
+  if (p.grp_tile) {
+    pdl_wait();
+    const int e = __ldg(p.grp_tile + tok_tile);
+    if (e < 0) return;   // whole CTA, before any barrier or TMEM allocation exists
+    w_row0 += e * p.n_out;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -447,7 +480,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       // weights first: they do not depend on the producer of x
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full[i], kTmaBytes);
-        tma_load_2d(smem + i * kStageBytes, &map_w, (kb0 + i) * kBlockK, m_tile * kBlockM, &full[i], w_policy);
+        tma_load_2d(smem + i * kStageBytes, &map_w, (kb0 + i) * kBlockK, w_row0, &full[i], w_policy);
       }
       tc_trace(p, 1);   // W of the first stages requested
     }
@@ -468,7 +501,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       mbar_wait(&empty[st], ((i / S) - 1) & 1);
       if (issuer) {
         mbar_expect_tx(&full[st], kTmaBytes);
-        tma_load_2d(smem + st * kStageBytes, &map_w, (kb0 + i) * kBlockK, m_tile * kBlockM, &full[st], w_policy);
+        tma_load_2d(smem + st * kStageBytes, &map_w, (kb0 + i) * kBlockK, w_row0, &full[st], w_policy);
         if constexpr (!NI)
           tma_load_2d(smem + st * kStageBytes + kABytes, &map_x, (kb0 + i) * kBlockK, tok_tile * N, &full[st], kEvictLast);
       }
@@ -1043,6 +1076,68 @@ int linear_tc(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, const
     case 64: return launch_tc<64>(mode, ni, mw, mx, p, pl, s);
     case 128: return launch_tc<128>(mode, ni, mw, mx, p, pl, s);
     default: return launch_tc<256>(mode, ni, mw, mx, p, pl, s);
+  }
+}
+
+// ---- grouped form: one launch over the tokens of every expert ---------------------------------------------------------
+// x [n_tiles * N][k] holds the gathered token rows, each expert's run padded to whole tiles of N rows; tile j belongs to
+// expert tile_expert[j] (device array; -1: unused).  w is [experts][n_out][k].  y != null: y[row][n_out] = bf16(x . w_e^T);
+// y == null: out[row_pair[row]][n_out] = (x . w_e^T) * wts[row_pair[row]] in fp32 (padding rows carry row_pair < 0).
+int linear_tc_grouped_tile(int pairs, int experts) {
+  const int avg = (pairs + experts - 1) / std::max(experts, 1);
+  return avg <= 16 ? 16 : (avg <= 32 ? 32 : (avg <= 64 ? 64 : 128));
+}
+
+bool linear_tc_grouped_supported(int n_out, int k) { return n_out > 0 && k > 0 && k % 8 == 0; }
+
+template <int N>
+static int launch_grouped(bool scatter, const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, const Plan& pl, cudaStream_t s) {
+  return scatter ? launch_tc3<N, kScatter, stages_for(N), false>(mw, mx, p, pl, s)
+                 : launch_tc3<N, kPlain, stages_for(N), false>(mw, mx, p, pl, s);
+}
+
+int linear_tc_grouped(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, const __nv_bfloat16* w, int experts, int n_out, int k,
+                      const int32_t* tile_expert, __nv_bfloat16* y, int64_t ldy, const int32_t* row_pair, const float* wts,
+                      float* out, cudaStream_t s) {
+  B200_REQUIRE(linear_tc_grouped_supported(n_out, k), B200_ERR_UNSUPPORTED, "linear_tc_grouped: k=%d must be a multiple of 8", k);
+  B200_REQUIRE(x && w && tile_expert && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   ldx % 8 == 0,
+               B200_ERR_INVALID, "linear_tc_grouped: operands must be 16-byte aligned");
+  B200_REQUIRE(N == 16 || N == 32 || N == 64 || N == 128, B200_ERR_INVALID, "linear_tc_grouped: token tile %d", N);
+  B200_REQUIRE(n_tiles > 0 && n_tiles <= 65535 && experts > 0, B200_ERR_INVALID, "linear_tc_grouped: %d tiles", n_tiles);
+  B200_REQUIRE(y || (row_pair && wts && out && reinterpret_cast<uintptr_t>(out) % 16 == 0), B200_ERR_INVALID,
+               "linear_tc_grouped: no destination");
+  Plan pl;
+  pl.N = N;
+  pl.m_tiles = (n_out + kBlockM - 1) / kBlockM;
+  pl.tok_tiles = n_tiles;
+  pl.n_kblocks = (k + kBlockK - 1) / kBlockK;
+  pl.splits = 1;
+  pl.n_out_pad = pl.m_tiles * kBlockM;
+  TcParams p = {};
+  p.trace = nullptr;
+  p.y = y;
+  p.ldy = ldy;
+  p.T = n_tiles * N;
+  p.n_out = n_out;
+  p.n_kblocks = pl.n_kblocks;
+  p.splits = 1;
+  p.n_out_pad = pl.n_out_pad;
+  p.grp_tile = tile_expert;
+  p.grp_pair = row_pair;
+  p.grp_wt = wts;
+  p.grp_out = out;
+  CUtensorMap mw, mx;
+  int rc = get_map(w, (uint64_t)experts * n_out, (uint64_t)k, (uint64_t)k, kBlockM, &mw);
+  if (rc) return rc;
+  rc = get_map(x, (uint64_t)n_tiles * N, (uint64_t)k, (uint64_t)ldx, (uint32_t)N, &mx);
+  if (rc) return rc;
+  const bool scatter = y == nullptr;
+  switch (N) {
+    case 16: return launch_grouped<16>(scatter, mw, mx, p, pl, s);
+    case 32: return launch_grouped<32>(scatter, mw, mx, p, pl, s);
+    case 64: return launch_grouped<64>(scatter, mw, mx, p, pl, s);
+    default: return launch_grouped<128>(scatter, mw, mx, p, pl, s);
   }
 }
 

@@ -10,9 +10,14 @@
 //  * token form (decode-sized steps): one CTA per (token, chosen slot) streams that expert's three matrices once;
 //  * grouped form (prefill-sized steps): tokens are bucketed by expert on the device (deterministic order: by token, then
 //    slot), and one CTA per (expert, tile of 16 of its tokens) streams the expert's weights once for the whole tile.
-// Both write one fp32 partial row per (token, slot), already multiplied by the mixing weight; the consumer (the norm that
+//  * tensor-core form (bf16 serving mode, width and ff multiples of 8; every step size): the (token, slot) pairs are
+//    grouped by expert into whole token tiles, the token rows gathered, and two launches of the grouped tcgen05 linear
+//    (gemm_tc.cu) run gate|up and down for all experts at once; the second one scatters the weighted fp32 rows.
+// All write one fp32 partial row per (token, slot), already multiplied by the mixing weight; the consumer (the norm that
 // follows the feed-forward) adds the slots in slot order, so the result does not depend on which form ran or on what else
 // was in the step beyond fp32 rounding.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -274,9 +279,127 @@ moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restr
   }
 }
 
+
+// ---- tensor-core form: grouping and gather --------------------------------------------------------------------------------
+// One CTA.  Counts per expert, then every expert's run starts on a tile boundary (tiles of N rows); tile_expert names the
+// owner of each tile (-1 past the last one), row_pair the (token, slot) pair of each row (-1 for the padding of a run).
+// Within a run the pairs keep their order (by token, then slot): a warp walks the pair list for its experts with ballots.
+constexpr int kGroupThreads = 1024;
+
+__global__ void __launch_bounds__(kGroupThreads)
+moe_group_kernel(const int32_t* __restrict__ ids, int n_pairs, int experts, int N, int n_tiles, int32_t* __restrict__ tile_expert,
+                 int32_t* __restrict__ row_pair) {
+  extern __shared__ int32_t gsm[];
+  int32_t* cnt = gsm;                  // [experts]
+  int32_t* start = cnt + experts;      // [experts] first row of the expert's run
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < experts; e += kGroupThreads) cnt[e] = 0;
+  for (int i = threadIdx.x; i < n_tiles * N; i += kGroupThreads) row_pair[i] = -1;
+  for (int i = threadIdx.x; i < n_tiles; i += kGroupThreads) tile_expert[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += kGroupThreads) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int nt = (cnt[e] + N - 1) / N;
+      start[e] = run * N;
+      for (int j = 0; j < nt && run + j < n_tiles; ++j) tile_expert[run + j] = e;
+      run += nt;
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = warp; e < experts; e += kGroupThreads / 32) {
+    if (cnt[e] == 0) continue;
+    int pos = start[e];
+    for (int b = 0; b < n_pairs; b += 32) {
+      const int i = b + lane;
+      const bool mine = i < n_pairs && ids[i] == e;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int r = pos + __popc(m & ((1u << lane) - 1u));
+        if (r < n_tiles * N) row_pair[r] = i;
+      }
+      pos += __popc(m);
+    }
+  }
+}
+
+// xg[row] = x[row_pair[row] / top] (zeros for padding rows); rows of unused tiles are left alone.  width % 8 == 0.
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ row_pair,
+                  int N, int top, int width, __nv_bfloat16* __restrict__ xg) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  if (tile_expert[row / N] < 0) return;
+  const int pair = row_pair[row];
+  const int chunks = width >> 3;
+  uint4* dst = reinterpret_cast<uint4*>(xg + (int64_t)row * width);
+  if (pair < 0) {
+    for (int c = threadIdx.x; c < chunks; c += 128) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(pair / top) * width);
+  for (int c = threadIdx.x; c < chunks; c += 128) dst[c] = __ldg(src + c);
+}
+
 }  // namespace
 
-int64_t moe_workspace_bytes(int T, int top, int experts) { return ((int64_t)T * top + experts + 8) * 4; }
+static int64_t al256(int64_t v) { return (v + 255) / 256 * 256; }
+
+// tensor-core form: rows and tiles of a step of T tokens (every expert's run padded to whole tiles of N rows)
+static void moe_tc_shape(int T, int top, int experts, int* N, int* n_tiles) {
+  const int pairs = T * top;
+  *N = linear_tc_grouped_tile(pairs, experts);
+  *n_tiles = pairs / *N + std::min(experts, pairs);
+}
+
+bool moe_tc_supported(int width, int ff) { return width % 8 == 0 && ff % 8 == 0; }
+
+// CUDA-core forms: the bucket lists.  Tensor-core form (width > 0, supported shape): tile and row tables, the gathered
+// rows, the gate|up rows and the activated rows, for any step of at most T tokens (at most pairs + experts * 128 rows).
+int64_t moe_workspace_bytes(int T, int top, int experts, int width, int ff) {
+  int64_t b = al256(((int64_t)T * top + experts + 8) * 4);
+  if (width > 0 && ff > 0 && moe_tc_supported(width, ff)) {
+    const int64_t rows = (int64_t)T * top + (int64_t)experts * 128, tiles = (int64_t)T * top / 16 + experts + 1;
+    b = std::max(b, al256(tiles * 4) + al256(rows * 4) + al256(rows * width * 2) + al256(rows * 2 * ff * 2) + al256(rows * ff * 2));
+  }
+  return b;
+}
+
+static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
+                          const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws,
+                          cudaStream_t s) {
+  int N, n_tiles;
+  moe_tc_shape(T, top, experts, &N, &n_tiles);
+  const int64_t rows = (int64_t)n_tiles * N;
+  char* p = static_cast<char*>(ws);
+  int32_t* tile_expert = reinterpret_cast<int32_t*>(p);
+  p += al256(((int64_t)T * top / 16 + experts + 1) * 4);
+  int32_t* row_pair = reinterpret_cast<int32_t*>(p);
+  p += al256(rows * 4);
+  __nv_bfloat16* xg = reinterpret_cast<__nv_bfloat16*>(p);
+  p += al256(rows * width * 2);
+  __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p);
+  p += al256(rows * 2 * ff * 2);
+  __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p);
+  B200_REQUIRE((size_t)experts * 8 <= 48 * 1024, B200_ERR_UNSUPPORTED, "experts: %d experts exceed the grouping kernel", experts);
+  B200_CUDA(launch(moe_group_kernel, dim3(1), dim3(kGroupThreads), (size_t)experts * 8, s, ids, T * top, experts, N, n_tiles,
+                   tile_expert, row_pair));
+  B200_CUDA(launch(moe_gather_kernel, dim3((unsigned)rows), dim3(128), (size_t)0, s, x, (const int32_t*)tile_expert,
+                   (const int32_t*)row_pair, N, top, width, xg));
+  int rc = linear_tc_grouped(xg, width, N, n_tiles, w_gu, experts, 2 * ff, width, tile_expert, gu, 2 * ff, nullptr, nullptr, nullptr, s);
+  if (rc) return rc;
+  rc = silu_mul(gu, act, (int)rows, ff, s);
+  if (rc) return rc;
+  return linear_tc_grouped(act, ff, N, n_tiles, w_down, experts, width, ff, tile_expert, nullptr, 0, row_pair, wts, parts, s);
+}
 
 int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
               int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s) {
@@ -329,6 +452,9 @@ static int moe_experts_t(const AT* x, const __nv_bfloat16* w_gu, const __nv_bflo
 int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
                 const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s) {
   if (T == 0) return B200_OK;
+  static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
+  if (!f32 && tc_env && ws && moe_tc_supported(width, ff))
+    return moe_experts_tc((const __nv_bfloat16*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, s);
   // an expert is chosen at most once per token, so it has at most T tokens: ceil(T / 16) tiles bound every expert
   const bool grouped = (int64_t)T * top >= 4 * (int64_t)experts && T >= 64;
   return f32 ? moe_experts_t<float>((const float*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, grouped, s)

@@ -46,8 +46,20 @@ struct StackModel {
   int32_t* route_ids = nullptr;
   float *route_w = nullptr, *parts = nullptr;
   void *attn_ws = nullptr, *moe_ws = nullptr;
+  void* attn_tc_ws = nullptr;   // row plan and split partials of the 128-wide tensor-core attention kernels
+  int64_t attn_tc_ws_bytes = 0;
   float* tap = nullptr;
 };
+
+bool paged_attn_tc_supported(int hq, int hkv, int block_size);   // attn_tc.cu
+
+// bf16 mode, 128-wide keys and values in blocks of 128 tokens: the tcgen05 attention kernels of the fixed decoder stack
+// serve the layer (bf16 queries, the output rotation as a step of its own); every other shape takes attn_anydim.cu
+static bool layer_attn_tc(const b200_stack_cfg& m, const b200_stack_layer& L) {
+  static const int env = getenv("B200_STACK_ATTN_TC") ? atoi(getenv("B200_STACK_ATTN_TC")) : 1;
+  return env && !m.f32 && L.dim == kHeadDim && L.vdim == kHeadDim && L.scale > 0.f &&
+         paged_attn_tc_supported(L.heads, L.kv_heads, m.block_size);
+}
 
 static int64_t up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
@@ -106,6 +118,11 @@ int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
   int attn_plan = (a.row_to_seq && T >= 32 && (a.n_seqs > 0 ? T >= 2 * a.n_seqs : true)) ? 1 : 0;
   static const int plan_env = getenv("B200_STACK_ATTN_RUNS") ? atoi(getenv("B200_STACK_ATTN_RUNS")) : 1;
   if (!plan_env) attn_plan = 0;
+  // the tensor-core kernels' view of the step (as in the fixed decoder stack): > 0 prefill-heavy, rows of a sequence
+  // share a pass over its K/V (2: the row plan for `pack_group` query heads per kv head is in the workspace); -1 decode only
+  int attn_pack = a.row_to_seq && (a.n_seqs > 0 ? (T >= 4 * a.n_seqs && T >= 32) : T >= 512);
+  if (!attn_pack && (a.row_to_seq == nullptr || a.n_seqs == T)) attn_pack = -1;
+  int pack_group = 0;
   STEP(embed_scaled(a.ids, M->embed, M->x, T, Wd, m.vocab, m.embed_scale, s, a.prev_tokens, a.n_prev));
   STEP(layernorm_stream(f32, M->x, nullptr, nullptr, 0, nullptr, M->w[0].n_mix_pre, M->hn, nullptr, T, Wd, m.norm_eps, s));
   for (int l = 0; l < nL; ++l) {
@@ -119,11 +136,32 @@ int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
     int64_t max_pos = 1ll << 40;
     if (rot) max_pos = std::min(max_pos, M->rot_pos[L.rot_table]);
     if (vrot) max_pos = std::min(max_pos, M->rot_pos[L.vrot_table]);
-    STEP(qk_norm_rotate_cache(f32, M->qkv, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, vrot, M->q, W.kc, W.vc, T,
-                              L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, max_pos, s));
-    STEP(paged_attn_anydim(f32, M->q, W.kc, W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, vrot, max_pos,
-                           M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, attn_plan, M->attn_ws, s));
-    if (attn_plan == 1) attn_plan = 2;
+    if (layer_attn_tc(m, L)) {
+      __nv_bfloat16* q16 = reinterpret_cast<__nv_bfloat16*>(M->q);
+      STEP(qk_norm_rotate_cache(f32, M->qkv, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, vrot, nullptr, W.kc, W.vc, T,
+                                L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, max_pos, s, q16));
+      int pack = attn_pack;
+      if (pack > 0) {
+        const int G = L.heads / L.kv_heads;
+        if (pack_group != G) {
+          const int built = paged_attn_prefill_plan_step(a.row_to_seq, a.ctx_lens, T, L.heads, L.kv_heads, m.block_size,
+                                                         M->attn_tc_ws, M->attn_tc_ws_bytes, s);
+          if (built < 0) return built;
+          pack_group = built == 1 ? G : 0;
+        }
+        pack = pack_group == G ? 2 : 1;
+      }
+      STEP(paged_attn_ex(q16, L.heads * L.dim, (const __nv_bfloat16*)W.kc, (const __nv_bfloat16*)W.vc, a.block_table, a.bt_stride,
+                         a.row_to_seq, a.ctx_lens, (__nv_bfloat16*)M->attn, L.heads * L.vdim, T, L.heads, L.kv_heads, m.block_size,
+                         a.max_ctx, L.scale, M->attn_tc_ws, M->attn_tc_ws_bytes, pack, s));
+      if (vrot) STEP(rotate_back_rows((__nv_bfloat16*)M->attn, a.positions, vrot, T, L.heads, L.vdim, max_pos, s));
+    } else {
+      STEP(qk_norm_rotate_cache(f32, M->qkv, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, vrot, M->q, W.kc, W.vc, T,
+                                L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, max_pos, s));
+      STEP(paged_attn_anydim(f32, M->q, W.kc, W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, vrot, max_pos,
+                             M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, attn_plan, M->attn_ws, s));
+      if (attn_plan == 1) attn_plan = 2;
+    }
     STEP(stack_linear(c, M->attn, L.heads * L.vdim, W.o, M->y, Wd, T, Wd, L.heads * L.vdim, s));
     if (L.mlp == B200_MLP_MOE) {
       STEP(layernorm_stream(f32, M->x, M->y, nullptr, 0, W.n_mix_post, W.n_mlp_pre, M->hn, nullptr, T, Wd, m.norm_eps, s));
@@ -163,6 +201,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
                    cfg->max_blocks_per_seq > 0 && cfg->max_logit_rows > 0,
                B200_ERR_INVALID, "stack_create: bad sizes");
   int max_qkv = 0, max_q = 0, max_a = 0, max_top = 0, max_exp = 0, max_ff = 0;
+  int64_t moe_ws_bytes = 16;
   for (int l = 0; l < cfg->n_layers; ++l) {
     const b200_stack_layer& L = layers[l];
     B200_REQUIRE(L.mixer == B200_MIXER_ATTENTION, B200_ERR_UNSUPPORTED, "stack_create: layer %d: unknown mixer %d", l, L.mixer);
@@ -179,6 +218,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       max_top = std::max(max_top, L.top);
       max_exp = std::max(max_exp, L.experts);
       max_ff = std::max(max_ff, L.ff);
+      moe_ws_bytes = std::max(moe_ws_bytes, moe_workspace_bytes(cfg->max_tokens, L.top, L.experts, cfg->f32 ? 0 : cfg->width, L.ff));
     }
     max_qkv = std::max(max_qkv, qkv_rows(L));
     max_q = std::max(max_q, L.heads * L.dim);
@@ -239,7 +279,17 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
   c->lin_ws_bytes = std::max<int64_t>(lw, 64 * 1024);
   c->meta_ints = 6 * T + T * cfg->max_blocks_per_seq;
   const int64_t attn_ws_bytes = paged_attn_anydim_workspace_bytes((int)T);
-  const int64_t moe_ws_bytes = max_top ? moe_workspace_bytes((int)T, max_top, max_exp) : 16;
+  int tc_heads = 0;
+  for (int l = 0; l < cfg->n_layers; ++l)
+    if (layer_attn_tc(*cfg, layers[l])) tc_heads = std::max(tc_heads, layers[l].heads);
+  M->attn_tc_ws_bytes = 16;
+  if (tc_heads) {
+    int max_ctx = 128;   // graph replay rounds a step's longest context up to a power of two
+    while (max_ctx < cfg->max_blocks_per_seq * cfg->block_size) max_ctx *= 2;
+    for (int t = 1; t <= T; t = t < 64 ? t + 1 : t * 2)   // the bound is not monotone in T: scan
+      M->attn_tc_ws_bytes = std::max(M->attn_tc_ws_bytes, paged_attn_workspace_bytes(t, tc_heads, max_ctx, cfg->block_size));
+    M->attn_tc_ws_bytes = std::max(M->attn_tc_ws_bytes, paged_attn_workspace_bytes((int)T, tc_heads, max_ctx, cfg->block_size));
+  }
 
   struct Item {
     void** p;
@@ -258,6 +308,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&M->lm_in, R * Wd * es},
       {(void**)&M->attn_ws, attn_ws_bytes},
       {(void**)&M->moe_ws, moe_ws_bytes},
+      {(void**)&M->attn_tc_ws, M->attn_tc_ws_bytes},
       {(void**)&c->logits, R * (int64_t)c->logits_ld * 2},
       {(void**)&c->logits_f32, cfg->f32 ? R * (int64_t)c->logits_ld * 4 : 16},
       {(void**)&c->lin_ws, c->lin_ws_bytes},
@@ -269,6 +320,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&c->d_adjust, (4ll << 20) * 4},
   };
   (void)max_ff;
+  (void)max_exp;
   int64_t total = 0;
   for (auto& it : items) total += up(std::max<int64_t>(it.bytes, 16), 1024);
   cudaError_t e = cudaMalloc(&c->pool, total);
@@ -431,7 +483,9 @@ extern "C" int b200_moe_route(int32_t f32, const void* x, const void* w_router, 
                    (cudaStream_t)stream);
 }
 
-extern "C" int64_t b200_moe_workspace_bytes(int32_t T, int32_t top, int32_t experts) { return moe_workspace_bytes(T, top, experts); }
+extern "C" int64_t b200_moe_workspace_bytes(int32_t T, int32_t top, int32_t experts, int32_t width, int32_t ff) {
+  return moe_workspace_bytes(T, top, experts, width, ff);
+}
 
 extern "C" int b200_moe_experts(int32_t f32, const void* x, const void* w_gu, const void* w_down, const int32_t* ids, const float* wts,
                                 int32_t T, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts, void* ws,

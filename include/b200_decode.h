@@ -450,8 +450,9 @@ B200_API int b200_paged_attn_anydim(int32_t f32, const float* q, const void* k_c
 /* Router: out_ids / out_weights [T][top].  bias may be NULL. */
 B200_API int b200_moe_route(int32_t f32, const void* x, const void* w_router, const float* bias, int32_t n_tokens, int32_t width,
                    int32_t experts, int32_t top, int32_t groups, int32_t keep, int32_t* out_ids, float* out_weights, void* stream);
-/* Chosen experts: parts [T][top][width] fp32, each row already times its weight.  workspace: b200_moe_workspace_bytes. */
-B200_API int64_t b200_moe_workspace_bytes(int32_t n_tokens, int32_t top, int32_t experts);
+/* Chosen experts: parts [T][top][width] fp32, each row already times its weight.  workspace: b200_moe_workspace_bytes
+   (width and ff > 0: room for the tensor-core form, which bf16 activations with width and ff multiples of 8 take). */
+B200_API int64_t b200_moe_workspace_bytes(int32_t n_tokens, int32_t top, int32_t experts, int32_t width, int32_t ff);
 B200_API int b200_moe_experts(int32_t f32, const void* x, const void* w_gate_up, const void* w_down, const int32_t* ids,
                      const float* weights, int32_t n_tokens, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts,
                      void* workspace, void* stream);

@@ -203,12 +203,56 @@ def test_experts_token_and_grouped_forms(f32, T, W, ff, experts, top):
     gu = torch.cat([torch.cat([gate[e], up[e]], 0) for e in range(experts)], 0)
     dn = torch.cat(down, 0)
     parts = torch.zeros(T, top, W, device=DEV)
-    ws = torch.zeros(int(lib().b200_moe_workspace_bytes(T, top, experts)), dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(int(lib().b200_moe_workspace_bytes(T, top, experts, W, ff)), dtype=torch.uint8, device=DEV)
     check(lib().b200_moe_experts(f32, dev(x).data_ptr(), dev(gu, torch.bfloat16).data_ptr(), dev(dn, torch.bfloat16).data_ptr(),
                                  dev(ids).data_ptr(), dev(wts).data_ptr(), T, W, ff, experts, top, parts.data_ptr(), ws.data_ptr(), None))
     sync()
     want = SO.experts(x.double(), ids.long(), wts.double(), [t.double() for t in gate], [t.double() for t in up], [t.double() for t in down])
-    assert torch.allclose(parts.cpu().double().sum(1), want, atol=3e-5)
+    # bf16 activations with width and ff multiples of 8 take the tensor-core form, which rounds gate|up and the activated
+    # rows to bf16 between its two products
+    tc = not f32 and W % 8 == 0 and ff % 8 == 0
+    assert torch.allclose(parts.cpu().double().sum(1), want, atol=3e-2 if tc else 3e-5)
+
+
+def _experts_rounded(x, ids, wts, gate, up, down):
+    """The tensor-core form's roundings: bf16 gate and up rows, bf16 silu, bf16 product, fp32 down rows times the weight."""
+    rb = lambda t: t.to(torch.bfloat16).double()
+    T, top = ids.shape
+    out = torch.zeros(T, top, down[0].shape[0], dtype=torch.float64)
+    for t in range(T):
+        for j in range(top):
+            e = int(ids[t, j])
+            gt, ut = rb(gate[e].double() @ x[t].double()), rb(up[e].double() @ x[t].double())
+            a = rb(rb(gt * torch.sigmoid(gt)) * ut)
+            out[t, j] = (down[e].double() @ a) * wts[t, j].double()
+    return out
+
+
+@pytest.mark.parametrize("T,W,ff,experts,top", [(1, 64, 64, 8, 2), (3, 136, 72, 5, 5), (40, 64, 200, 4, 2), (300, 256, 136, 6, 3),
+                                                (700, 128, 64, 3, 1)])
+def test_experts_tensor_core_form(T, W, ff, experts, top):
+    """Every token-tile size, runs that end inside a tile, experts nobody chose, slab rows past an expert's last row."""
+    g = torch.Generator().manual_seed(T + W)
+    x = torch.randn(T, W, generator=g).to(torch.bfloat16)
+    gate = [U.bf16_exact(torch.randn(ff, W, generator=g) * W ** -0.5) for _ in range(experts)]
+    up = [U.bf16_exact(torch.randn(ff, W, generator=g) * W ** -0.5) for _ in range(experts)]
+    down = [U.bf16_exact(torch.randn(W, ff, generator=g) * ff ** -0.5) for _ in range(experts)]
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    if top == 1:
+        ids[ids == experts - 1] = 0   # the last expert gets no token
+    wts = torch.rand(T, top, generator=g)
+    gu = torch.cat([torch.cat([gate[e], up[e]], 0) for e in range(experts)], 0)
+    dn = torch.cat(down, 0)
+    parts = torch.full((T, top, W), float("nan"), device=DEV)
+    ws = torch.zeros(int(lib().b200_moe_workspace_bytes(T, top, experts, W, ff)), dtype=torch.uint8, device=DEV)
+    for _ in range(2):   # the second call finds the first one's tables in the workspace
+        check(lib().b200_moe_experts(0, dev(x).data_ptr(), dev(gu, torch.bfloat16).data_ptr(), dev(dn, torch.bfloat16).data_ptr(),
+                                     dev(ids).data_ptr(), dev(wts).data_ptr(), T, W, ff, experts, top, parts.data_ptr(), ws.data_ptr(), None))
+    sync()
+    want = _experts_rounded(x, ids, wts, gate, up, down)
+    got = parts.cpu().double()
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, atol=4e-3, rtol=4e-3)
 
 
 @pytest.mark.parametrize("T,n,k", [(1, 5, 7), (70, 130, 33), (64, 64, 16)])
@@ -300,6 +344,39 @@ def test_bf16_mode_within_bf16_noise_and_equal_across_schedules(model_a):
         d = U.rel_rms(mixed[n], whole[n])      # the same arithmetic up to summation order (and a rare router near-tie)
         assert np.median(d) < 0.02 and (d < 0.1).mean() > 0.9, (n, float(np.median(d)), float(d.max()))
     r.close()
+
+
+WIDE = dict(width=128, vocab=160, scale=1.5, eps=1e-5, layers=[
+    U.layer(heads=4, kv_heads=1, dim=128, vdim=128, rot_dims=64, att_scale=0.09, moe=dict(experts=8, top=2, groups=2, keep=1, ff=64)),
+    U.layer(heads=2, kv_heads=2, dim=128, vdim=128, rot_dims=128, scaling=None, att_scale=0.12, moe=None),
+    U.layer(heads=4, kv_heads=2, dim=64, vdim=128, rot_dims=32, att_scale=0.12, moe=dict(experts=4, top=1, groups=1, keep=1, ff=72))])
+
+
+def test_128_wide_heads_take_the_tensor_core_attention_and_agree_with_the_generic_kernels():
+    """bf16 mode with blocks of 128 tokens: layers with 128-wide keys and values run the tcgen05 attention kernels (two group
+    sizes in one model, so the row plan is rebuilt between layers), the third layer keeps the generic kernels.  Against the
+    oracle within bf16 noise, against the same model in blocks of 16 (generic kernels everywhere), and across schedules:
+    keys beyond one and two blocks, portions that end at and next to a block border, decoding over a border."""
+    cfg = U.make_cfg(**WIDE)
+    w = U.make_weights(cfg, seed=13)
+    prompts = {"a": _prompt(cfg, 300, 6), "b": _prompt(cfg, 131, 7), "c": _prompt(cfg, 40, 8)}
+    want = {n: SO.forward(cfg, w, p).numpy() for n, p in prompts.items()}
+    r = U.make_runner(cfg, w, "bfloat16", block_size=128, n_blocks=6, max_tokens=512, max_model_len=512)
+    eng = U.make_engine(r)
+    whole = U.replay(eng, [[("a", 300)], [("b", 131)], [("c", 40)]], prompts)
+    mixed = U.replay(eng, [[("a", 127), ("b", 2)], [("a", 1), ("b", 126), ("c", 38)], [("a", 130), ("b", 1), ("c", 1)]] +
+                     [[("a", 1), ("b", 1), ("c", 1)]] + [[("a", 1), ("b", 1)]] + [[("a", 1)]] * 20 + [[("a", 20)]], prompts)
+    assert len(eng.blocks.free) == 6
+    r.close()
+    r16 = U.make_runner(cfg, w, "bfloat16", block_size=16, n_blocks=40, max_tokens=512, max_model_len=512)
+    small = U.replay(U.make_engine(r16), [[("a", 300)], [("b", 131)], [("c", 40)]], prompts)
+    r16.close()
+    for n in prompts:
+        e = U.rel_rms(whole[n], want[n])
+        assert np.median(e) < 0.03 and (e < 0.1).mean() > 0.9, (n, float(np.median(e)), float(e.max()))
+        for other in (mixed, small):
+            d = U.rel_rms(other[n], whole[n])
+            assert np.median(d) < 0.03 and (d < 0.1).mean() > 0.9, (n, float(np.median(d)), float(d.max()))
 
 
 def test_greedy_generation_through_the_engines_own_scheduler(model_odd, tmp_path):
