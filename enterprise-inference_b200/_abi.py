@@ -109,6 +109,7 @@ SIGNATURES = {
     "b200_paged_attn_anydim": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _i32,
                                          _i32, _f32, _i32, _vp, _vp]),
     "b200_moe_route": (C.c_int, [_i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "b200_moe_route_linear": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "b200_moe_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32, _i32]),
     "b200_moe_experts": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "b200_linear_simt": (C.c_int, [_i32, _i32, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),

@@ -174,7 +174,8 @@ int linear_gemv(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, con
 bool linear_tc_supported(int T, int n_out, int k);
 int64_t linear_tc_workspace_bytes(int T, int n_out, int k);
 // Optional fusions of the tcgen05 linear.  Epilogue modes: 0 plain, 1 silu*mul over an interleaved gate|up slab,
-// 2 RoPE + KV append over a fused qkv projection, 3 add into the fp32 residual stream (sres/ssq, no y).
+// 2 RoPE + KV append over a fused qkv projection, 3 add into the fp32 residual stream (sres/ssq, no y),
+// 4 unrounded fp32 output rows in out_f32 [T][n_out] (no y).
 // norm_in: the input rows are not read from x but normalised on the fly from the fp32 residual stream
 // (RMSNorm folded into the consumer: sres, ssq, norm_w, eps, optional row indirection `rows`).
 struct LinearExtra {
@@ -191,6 +192,7 @@ struct LinearExtra {
   __nv_bfloat16* kc = nullptr;
   __nv_bfloat16* vc = nullptr;
   int hq = 0, hkv = 0, block_size = 0;
+  float* out_f32 = nullptr;
 };
 int linear_tc(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, const __nv_bfloat16* bias,
               __nv_bfloat16* y, int64_t ldy, int T, int n_out, int k, void* ws, int64_t ws_bytes,
@@ -285,8 +287,10 @@ int paged_attn_anydim(bool f32, const float* q, const void* kc, const void* vc, 
 // mixture of experts (moe.cu)
 int64_t moe_workspace_bytes(int T, int top, int experts, int width, int ff);
 bool moe_tc_supported(int width, int ff);
+// logits_ws ([T][experts] fp32) given and bf16 rows: the logits come from the tcgen05 linear (lin_ws: its split-K workspace)
 int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
-              int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s);
+              int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s, float* logits_ws = nullptr,
+              void* lin_ws = nullptr, int64_t lin_ws_bytes = 0);
 int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
                 const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s);
 // true-fp32 CUDA-core linear (linear_simt.cu)

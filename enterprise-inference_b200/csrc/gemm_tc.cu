@@ -186,10 +186,19 @@ struct TcParams {
   const int32_t* grp_tile;
   // kScatter: row t of the launch goes to grp_out[grp_pair[t]][n_out] (fp32, unrounded) times grp_wt[grp_pair[t]];
   // grp_pair[t] < 0 marks a padding row
+  // (both null: the identity and weight 1, i.e. a plain fp32 output)
   const int32_t* grp_pair;
   const float* grp_wt;
   float* grp_out;
+  int tile_n;            // N of the instantiation (kScatter: index of a token inside its tile)
 };
+
+// kScatter: the tile's destination rows and weights, fetched once per CTA before the accumulator is complete (the two
+// dependent global loads per token would otherwise sit between the TMEM drain and every store)
+__device__ __forceinline__ int* scatter_smem() {
+  __shared__ int buf[512];   // [256] destination row | [256] weight (float bits)
+  return buf;
+}
 
 __device__ __forceinline__ void tc_trace(const TcParams& p, int slot) {
 #ifndef B200_TRACE_BUILD
@@ -220,7 +229,7 @@ template <int MODE>
 __device__ __forceinline__ void finalize4(const TcParams& p, int m_tile, int lane, int tok, float4 a, const float (&bb)[4]) {
   const int r4 = lane * 4;
   float v[4] = {round_bf16(a.x + bb[0]), round_bf16(a.y + bb[1]), round_bf16(a.z + bb[2]), round_bf16(a.w + bb[3])};
-  if (MODE == kPlain) {
+  if constexpr (MODE == kPlain) {
     const int row = m_tile * kBlockM + r4;
     __nv_bfloat16* dst = p.y + (int64_t)tok * p.ldy + row;
     if (row + 3 < p.n_out && (p.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 7) == 0)) {
@@ -230,7 +239,7 @@ __device__ __forceinline__ void finalize4(const TcParams& p, int m_tile, int lan
       for (int e = 0; e < 4; ++e)
         if (row + e < p.n_out) dst[e] = __float2bfloat16_rn(v[e]);
     }
-  } else if (MODE == kSiluMul) {
+  } else if constexpr (MODE == kSiluMul) {
     // lanes 0..15 hold 4 gate rows, lanes 16..31 the 4 matching up rows: after the exchange every lane has
     // both, and each half-warp finalises two of the four features (all 32 lanes busy: the accurate
     // expf + division of R5 is what this epilogue costs at large T)
@@ -249,7 +258,7 @@ __device__ __forceinline__ void finalize4(const TcParams& p, int m_tile, int lan
       dst[0] = __float2bfloat16_rn(o0);
       dst[1] = __float2bfloat16_rn(o1);
     }
-  } else if (MODE == kResidual) {
+  } else if constexpr (MODE == kResidual) {
     // x = bf16(acc + bias); s = x + bf16(s_old) in fp32 (R1: the residual is kept in bf16, the sum is not rounded
     // before the variance and the normalisation); sum of squares in a fixed order: lane's 4 rows, then the warp tree
     const int row = m_tile * kBlockM + r4;
@@ -264,10 +273,12 @@ __device__ __forceinline__ void finalize4(const TcParams& p, int m_tile, int lan
     ss = fmaf(sn.w, sn.w, ss);
     ss = warp_sum(ss);
     if (lane == 0) p.ssq[(int64_t)tok * p.nslab + m_tile] = ss;
-  } else if (MODE == kScatter) {
-    const int pair = __ldg(p.grp_pair + tok);   // warp-uniform
+  } else if constexpr (MODE == kScatter) {
+    const int* sc = scatter_smem();
+    const int tl = tok % p.tile_n;
+    const int pair = sc[tl];   // warp-uniform
     if (pair < 0) return;
-    const float wt = __ldg(p.grp_wt + pair);
+    const float wt = __int_as_float(sc[256 + tl]);
     const int row = m_tile * kBlockM + r4;
     float* dst = p.grp_out + (int64_t)pair * p.n_out + row;
     if (row + 3 < p.n_out && (p.n_out % 4 == 0)) {
@@ -546,6 +557,21 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int tok0 = tok_tile * N;
     const int wq = warp - 2;
     pdl_wait();
+    if constexpr (MODE == kScatter) {
+      int* sc = scatter_smem();
+      for (int t = wq * 32 + lane; t < N; t += 128) {
+        const int tok = tok0 + t;
+        int pair = -1;
+        float wt = 1.0f;
+        if (tok < p.T) {
+          pair = p.grp_pair ? __ldg(p.grp_pair + tok) : tok;
+          if (pair >= 0 && p.grp_wt) wt = __ldg(p.grp_wt + pair);
+        }
+        sc[t] = pair;
+        sc[256 + t] = __float_as_int(wt);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     if constexpr (NI) norm_b_tiles<N, S>(p, smem, full, empty, rinv_s, tok0, kb0, nkb, wq, lane);
     if (nkb > 0) {
       mbar_wait(tmem_full, 0);
@@ -965,6 +991,7 @@ int launch_tc(int mode, bool ni, const CUtensorMap& mw, const CUtensorMap& mx, c
   }
   B200_REQUIRE(mode != kResidual && !ni, B200_ERR_UNSUPPORTED, "linear_tc: the fused-norm modes need T <= 64 (T tile %d)", N);
   switch (mode) {
+    case kScatter: return launch_tc2<N, kScatter, false>(mw, mx, p, pl, s);
     case kSiluMul: return launch_tc2<N, kSiluMul, false>(mw, mx, p, pl, s);
     case kRopeKv: return launch_tc2<N, kRopeKv, false>(mw, mx, p, pl, s);
     default: return launch_tc2<N, kPlain, false>(mw, mx, p, pl, s);
@@ -1036,6 +1063,9 @@ int linear_tc(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, const
     p.sres = ex->sres;
     p.ssq = ex->ssq;
     p.nslab = n_out / kBlockM;
+  } else if (mode == kScatter) {
+    B200_REQUIRE(ex->out_f32 && reinterpret_cast<uintptr_t>(ex->out_f32) % 16 == 0, B200_ERR_INVALID, "linear_tc(f32 out): no output");
+    p.grp_out = ex->out_f32;   // y[t][row] stays unrounded: row stride n_out
   } else {
     B200_REQUIRE(mode == kPlain, B200_ERR_INVALID, "linear_tc: unknown epilogue mode %d", mode);
   }
@@ -1070,6 +1100,7 @@ int linear_tc(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, const
   p.tickets = reinterpret_cast<unsigned int*>(ws);
   p.partials = ws ? reinterpret_cast<float*>(static_cast<char*>(ws) + kCounterBytes) : nullptr;
   p.n_out_pad = pl.n_out_pad;
+  p.tile_n = pl.N;
   switch (pl.N) {
     case 16: return launch_tc<16>(mode, ni, mw, mx, p, pl, s);
     case 32: return launch_tc<32>(mode, ni, mw, mx, p, pl, s);
@@ -1127,6 +1158,7 @@ int linear_tc_grouped(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, c
   p.grp_pair = row_pair;
   p.grp_wt = wts;
   p.grp_out = out;
+  p.tile_n = N;
   CUtensorMap mw, mx;
   int rc = get_map(w, (uint64_t)experts * n_out, (uint64_t)k, (uint64_t)k, kBlockM, &mw);
   if (rc) return rc;

@@ -44,29 +44,10 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-template <typename AT>
-__global__ void __launch_bounds__(kRouteThreads)
-moe_route_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ wr, const float* __restrict__ bias, int width,
-                 int experts, int top, int groups, int keep, int32_t* __restrict__ out_ids, float* __restrict__ out_w) {
-  extern __shared__ float sm[];
-  float* xs = sm;                 // [width]
-  float* sc = xs + width;         // [experts] softmax scores
-  float* ch = sc + experts;       // [experts] choice scores (eligible) / -inf
-  float* gs = ch + experts;       // [groups]
-  pdl_wait();
-  pdl_launch_dependents();
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kRouteThreads / 32;
-  for (int c = threadIdx.x; c < width; c += kRouteThreads) xs[c] = ld_act<AT>(x, (int64_t)t * width + c);
-  __syncthreads();
-  for (int e = warp; e < experts; e += nw) {
-    const __nv_bfloat16* w = wr + (int64_t)e * width;
-    float a = 0.f;
-    for (int c = lane; c < width; c += 32) a = fmaf(__bfloat162float(w[c]), xs[c], a);
-    a = warp_sum(a);
-    if (lane == 0) sc[e] = a;
-  }
-  __syncthreads();
-  if (warp != 0) return;
+// One warp: softmax over the logits in sc[experts] (replaced by the scores), choice scores in ch, the group limit, top-k.
+__device__ __forceinline__ void route_select(float* sc, float* ch, float* gs, const float* __restrict__ bias, int lane, int t,
+                                             int experts, int top, int groups, int keep, int32_t* __restrict__ out_ids,
+                                             float* __restrict__ out_w) {
   float mx = -INFINITY;
   for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, sc[e]);
   mx = warp_max(mx);
@@ -131,6 +112,51 @@ moe_route_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
     }
     __syncwarp();
   }
+}
+
+// Selection over logits that a linear already produced ([T][experts] fp32): one warp per token.
+constexpr int kSelWarps = 4;
+__global__ void __launch_bounds__(kSelWarps * 32)
+moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int experts, int top, int groups,
+                  int keep, int32_t* __restrict__ out_ids, float* __restrict__ out_w) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kSelWarps + warp;
+  if (t >= T) return;
+  float* sc = sm + (size_t)warp * (2 * experts + groups);
+  float* ch = sc + experts;
+  float* gs = ch + experts;
+  for (int e = lane; e < experts; e += 32) sc[e] = logits[(int64_t)t * experts + e];
+  __syncwarp();
+  route_select(sc, ch, gs, bias, lane, t, experts, top, groups, keep, out_ids, out_w);
+}
+
+template <typename AT>
+__global__ void __launch_bounds__(kRouteThreads)
+moe_route_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ wr, const float* __restrict__ bias, int width,
+                 int experts, int top, int groups, int keep, int32_t* __restrict__ out_ids, float* __restrict__ out_w) {
+  extern __shared__ float sm[];
+  float* xs = sm;                 // [width]
+  float* sc = xs + width;         // [experts] softmax scores
+  float* ch = sc + experts;       // [experts] choice scores (eligible) / -inf
+  float* gs = ch + experts;       // [groups]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kRouteThreads / 32;
+  for (int c = threadIdx.x; c < width; c += kRouteThreads) xs[c] = ld_act<AT>(x, (int64_t)t * width + c);
+  __syncthreads();
+  for (int e = warp; e < experts; e += nw) {
+    const __nv_bfloat16* w = wr + (int64_t)e * width;
+    float a = 0.f;
+    for (int c = lane; c < width; c += 32) a = fmaf(__bfloat162float(w[c]), xs[c], a);
+    a = warp_sum(a);
+    if (lane == 0) sc[e] = a;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  route_select(sc, ch, gs, bias, lane, t, experts, top, groups, keep, out_ids, out_w);
 }
 
 // ---- token form ---------------------------------------------------------------------------------------------------------
@@ -285,6 +311,7 @@ moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restr
 // owner of each tile (-1 past the last one), row_pair the (token, slot) pair of each row (-1 for the padding of a run).
 // Within a run the pairs keep their order (by token, then slot): a warp walks the pair list for its experts with ballots.
 constexpr int kGroupThreads = 1024;
+constexpr int kGroupChunk = 8192;
 
 __global__ void __launch_bounds__(kGroupThreads)
 moe_group_kernel(const int32_t* __restrict__ ids, int n_pairs, int experts, int N, int n_tiles, int32_t* __restrict__ tile_expert,
@@ -313,19 +340,30 @@ moe_group_kernel(const int32_t* __restrict__ ids, int n_pairs, int experts, int 
     }
   }
   __syncthreads();
+  // the pair list goes through shared memory a chunk at a time: the walk below is a chain of ballots, and a global load
+  // inside it would pay its latency once per 32 pairs
+  int32_t* chunk = start + experts;   // [kGroupChunk]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int e = warp; e < experts; e += kGroupThreads / 32) {
-    if (cnt[e] == 0) continue;
-    int pos = start[e];
-    for (int b = 0; b < n_pairs; b += 32) {
-      const int i = b + lane;
-      const bool mine = i < n_pairs && ids[i] == e;
-      const unsigned m = __ballot_sync(0xffffffffu, mine);
-      if (mine) {
-        const int r = pos + __popc(m & ((1u << lane) - 1u));
-        if (r < n_tiles * N) row_pair[r] = i;
+  for (int c0 = 0; c0 < n_pairs; c0 += kGroupChunk) {
+    const int cn = min(kGroupChunk, n_pairs - c0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < cn; i += kGroupThreads) chunk[i] = ids[c0 + i];
+    __syncthreads();
+    for (int e = warp; e < experts; e += kGroupThreads / 32) {
+      if (cnt[e] == 0) continue;
+      int pos = start[e];
+      for (int b = 0; b < cn; b += 32) {
+        const int i = b + lane;
+        const bool mine = i < cn && chunk[i] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+          const int r = pos + __popc(m & ((1u << lane) - 1u));
+          if (r < n_tiles * N) row_pair[r] = c0 + i;
+        }
+        pos += __popc(m);
       }
-      pos += __popc(m);
+      __syncwarp();
+      if (lane == 0) start[e] = pos;   // this warp alone owns expert e
     }
   }
 }
@@ -389,8 +427,8 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
   __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p);
   p += al256(rows * 2 * ff * 2);
   __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p);
-  B200_REQUIRE((size_t)experts * 8 <= 48 * 1024, B200_ERR_UNSUPPORTED, "experts: %d experts exceed the grouping kernel", experts);
-  B200_CUDA(launch(moe_group_kernel, dim3(1), dim3(kGroupThreads), (size_t)experts * 8, s, ids, T * top, experts, N, n_tiles,
+  B200_REQUIRE(experts <= 1024, B200_ERR_UNSUPPORTED, "experts: %d experts exceed the grouping kernel", experts);
+  B200_CUDA(launch(moe_group_kernel, dim3(1), dim3(kGroupThreads), (size_t)experts * 8 + (size_t)kGroupChunk * 4, s, ids, T * top, experts, N, n_tiles,
                    tile_expert, row_pair));
   B200_CUDA(launch(moe_gather_kernel, dim3((unsigned)rows), dim3(128), (size_t)0, s, x, (const int32_t*)tile_expert,
                    (const int32_t*)row_pair, N, top, width, xg));
@@ -402,12 +440,29 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
 }
 
 int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
-              int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s) {
+              int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s, float* logits_ws, void* lin_ws,
+              int64_t lin_ws_bytes) {
   if (T == 0) return B200_OK;
   B200_REQUIRE(experts > 0 && top > 0 && top <= experts, B200_ERR_INVALID, "router: top %d of %d experts", top, experts);
   if (groups < 1) groups = 1;
   B200_REQUIRE(experts % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (experts / groups), B200_ERR_INVALID,
                "router: %d experts in %d groups, keep %d, top %d", experts, groups, keep, top);
+  static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
+  const size_t smem_sel = (size_t)kSelWarps * (2 * experts + groups) * 4;
+  if (!f32 && tc_env && logits_ws && width % 8 == 0 && reinterpret_cast<uintptr_t>(w_router) % 16 == 0 && smem_sel <= 48 * 1024 &&
+      linear_tc_supported(T, experts, width) && (lin_ws == nullptr || linear_tc_workspace_bytes(T, experts, width) <= lin_ws_bytes)) {
+    // bf16 rows: the logits are a tcgen05 linear with unrounded fp32 output (bf16 products are exact in fp32, the sum is
+    // fp32), then one warp per token selects
+    LinearExtra ex;
+    ex.mode = 4;
+    ex.out_f32 = logits_ws;
+    const int rc = linear_tc((const __nv_bfloat16*)x, width, w_router, nullptr, nullptr, experts, T, experts, width, lin_ws,
+                             lin_ws_bytes, &ex, s);
+    if (rc) return rc;
+    B200_CUDA(launch(moe_select_kernel, dim3((T + kSelWarps - 1) / kSelWarps), dim3(kSelWarps * 32), smem_sel, s,
+                     (const float*)logits_ws, bias, T, experts, top, groups, keep, out_ids, out_w));
+    return B200_OK;
+  }
   const size_t smem = ((size_t)width + 2 * experts + groups) * 4;
   B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "router: row of %zu bytes does not fit shared memory", smem);
   static bool done[2][64] = {};

@@ -44,7 +44,7 @@ struct StackModel {
   void *hn = nullptr, *qkv = nullptr, *attn = nullptr, *y = nullptr, *lm_in = nullptr;
   float* q = nullptr;
   int32_t* route_ids = nullptr;
-  float *route_w = nullptr, *parts = nullptr;
+  float *route_w = nullptr, *parts = nullptr, *route_logits = nullptr;
   void *attn_ws = nullptr, *moe_ws = nullptr;
   void* attn_tc_ws = nullptr;   // row plan and split partials of the 128-wide tensor-core attention kernels
   int64_t attn_tc_ws_bytes = 0;
@@ -165,7 +165,8 @@ int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
     STEP(stack_linear(c, M->attn, L.heads * L.vdim, W.o, M->y, Wd, T, Wd, L.heads * L.vdim, s));
     if (L.mlp == B200_MLP_MOE) {
       STEP(layernorm_stream(f32, M->x, M->y, nullptr, 0, W.n_mix_post, W.n_mlp_pre, M->hn, nullptr, T, Wd, m.norm_eps, s));
-      STEP(moe_route(f32, M->hn, W.router, W.router_bias, T, Wd, L.experts, L.top, L.groups, L.keep, M->route_ids, M->route_w, s));
+      STEP(moe_route(f32, M->hn, W.router, W.router_bias, T, Wd, L.experts, L.top, L.groups, L.keep, M->route_ids, M->route_w, s,
+                     M->route_logits, c->lin_ws, c->lin_ws_bytes));
       STEP(moe_experts(f32, M->hn, W.e_gate_up, W.e_down, M->route_ids, M->route_w, T, Wd, L.ff, L.experts, L.top, M->parts,
                        M->moe_ws, s));
       STEP(layernorm_stream(f32, M->x, nullptr, M->parts, L.top, W.n_mlp_post, next_pre, M->hn, nullptr, T, Wd, m.norm_eps, s));
@@ -263,6 +264,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     for (int l = 0; l < cfg->n_layers; ++l) {
       shapes.push_back({qkv_rows(layers[l]), (int)Wd});
       shapes.push_back({(int)Wd, layers[l].heads * layers[l].vdim});
+      if (layers[l].mlp == B200_MLP_MOE) shapes.push_back({layers[l].experts, (int)Wd});
     }
     for (auto& sh : shapes) {
       if (sh.second % 8) continue;
@@ -305,6 +307,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&M->route_ids, T * std::max(max_top, 1) * 4},
       {(void**)&M->route_w, T * std::max(max_top, 1) * 4},
       {(void**)&M->parts, T * std::max(max_top, 1) * Wd * 4},
+      {(void**)&M->route_logits, T * std::max(max_exp, 1) * 4},
       {(void**)&M->lm_in, R * Wd * es},
       {(void**)&M->attn_ws, attn_ws_bytes},
       {(void**)&M->moe_ws, moe_ws_bytes},
@@ -320,7 +323,6 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&c->d_adjust, (4ll << 20) * 4},
   };
   (void)max_ff;
-  (void)max_exp;
   int64_t total = 0;
   for (auto& it : items) total += up(std::max<int64_t>(it.bytes, 16), 1024);
   cudaError_t e = cudaMalloc(&c->pool, total);
@@ -481,6 +483,14 @@ extern "C" int b200_moe_route(int32_t f32, const void* x, const void* w_router, 
   B200_REQUIRE(x && w_router && out_ids && out_w && width > 0, B200_ERR_INVALID, "moe_route: bad argument");
   return moe_route(f32 != 0, x, (const __nv_bfloat16*)w_router, bias, T, width, experts, top, groups, keep, out_ids, out_w,
                    (cudaStream_t)stream);
+}
+
+extern "C" int b200_moe_route_linear(const void* x, const void* w_router, const float* bias, int32_t T, int32_t width, int32_t experts,
+                                     int32_t top, int32_t groups, int32_t keep, int32_t* out_ids, float* out_w, float* logits,
+                                     void* stream) {
+  B200_REQUIRE(x && w_router && out_ids && out_w && logits && width > 0, B200_ERR_INVALID, "moe_route_linear: bad argument");
+  return moe_route(false, x, (const __nv_bfloat16*)w_router, bias, T, width, experts, top, groups, keep, out_ids, out_w,
+                   (cudaStream_t)stream, logits, nullptr, 0);
 }
 
 extern "C" int64_t b200_moe_workspace_bytes(int32_t T, int32_t top, int32_t experts, int32_t width, int32_t ff) {

@@ -450,6 +450,10 @@ B200_API int b200_paged_attn_anydim(int32_t f32, const float* q, const void* k_c
 /* Router: out_ids / out_weights [T][top].  bias may be NULL. */
 B200_API int b200_moe_route(int32_t f32, const void* x, const void* w_router, const float* bias, int32_t n_tokens, int32_t width,
                    int32_t experts, int32_t top, int32_t groups, int32_t keep, int32_t* out_ids, float* out_weights, void* stream);
+/* The same router over bf16 rows with the logits from the tcgen05 linear: logits [n_tokens][experts] fp32 is written too. */
+B200_API int b200_moe_route_linear(const void* x, const void* w_router, const float* bias, int32_t n_tokens, int32_t width,
+                                   int32_t experts, int32_t top, int32_t groups, int32_t keep, int32_t* out_ids, float* out_w,
+                                   float* logits, void* stream);
 /* Chosen experts: parts [T][top][width] fp32, each row already times its weight.  workspace: b200_moe_workspace_bytes
    (width and ff > 0: room for the tensor-core form, which bf16 activations with width and ff multiples of 8 take). */
 B200_API int64_t b200_moe_workspace_bytes(int32_t n_tokens, int32_t top, int32_t experts, int32_t width, int32_t ff);

@@ -189,6 +189,28 @@ def test_router_against_the_oracle(experts, top, groups, keep):
     assert torch.allclose(got, torch.zeros(T, experts, dtype=torch.float64).scatter_(1, wi, ww), atol=1e-6)
 
 
+@pytest.mark.parametrize("T,W,experts,top,groups,keep", [(1, 72, 8, 3, 4, 2), (40, 136, 12, 4, 3, 3), (300, 64, 64, 6, 8, 3), (17, 520, 132, 5, 1, 1)])
+def test_router_with_tensor_core_logits(T, W, experts, top, groups, keep):
+    """bf16 rows: logits from the tcgen05 linear with fp32 output (one and several token tiles, more experts than a slab),
+    then the per-token selection.  The logits against float64, the choice against the oracle."""
+    g = torch.Generator().manual_seed(T)
+    x = U.bf16_exact(torch.randn(T, W, generator=g))
+    wr = U.bf16_exact(torch.randn(experts, W, generator=g) * 0.5)
+    bias = torch.randn(experts, generator=g) * 0.3 - 0.5
+    ids = torch.zeros(T, top, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(T, top, device=DEV)
+    logits = torch.full((T, experts), float("nan"), device=DEV)
+    check(lib().b200_moe_route_linear(dev(x, torch.bfloat16).data_ptr(), dev(wr, torch.bfloat16).data_ptr(), dev(bias).data_ptr(), T, W,
+                                      experts, top, groups, keep, ids.data_ptr(), wts.data_ptr(), logits.data_ptr(), None))
+    sync()
+    assert torch.allclose(logits.cpu().double(), x.double() @ wr.double().T, atol=1e-4, rtol=1e-5)
+    r = dict(experts=experts, top=top, groups=dict(count=groups, keep=keep))
+    wi, ww = SO.route(x.double(), wr.double(), bias.double(), r)
+    assert torch.equal(ids.cpu().long().sort(-1).values, wi.sort(-1).values)
+    got = torch.zeros(T, experts, dtype=torch.float64).scatter_(1, ids.cpu().long(), wts.cpu().double())
+    assert torch.allclose(got, torch.zeros(T, experts, dtype=torch.float64).scatter_(1, wi, ww), atol=1e-6)
+
+
 @pytest.mark.parametrize("f32", [1, 0])
 @pytest.mark.parametrize("T,W,ff,experts,top", [(5, 72, 40, 6, 2), (150, 96, 24, 4, 3), (70, 64, 130, 3, 1)])
 def test_experts_token_and_grouped_forms(f32, T, W, ff, experts, top):
