@@ -99,6 +99,7 @@ SIGNATURES = {
     "b200_stack_create": (C.c_int, [C.POINTER(StackCfg), C.POINTER(StackLayer), C.POINTER(_vp)]),
     "b200_stack_set_weight": (C.c_int, [_vp, _i32, _i32, _vp, _i64, _i64]),
     "b200_stack_set_kv_cache": (C.c_int, [_vp, _i32, _vp, _vp, _i64]),
+    "b200_stack_cache_dims": (C.c_int, [_vp, _i32, _vp, _vp]),
     "b200_stack_set_rot_table": (C.c_int, [_vp, _i32, _vp, _i64, _i32]),
     "b200_stack_set_stream_tap": (C.c_int, [_vp, _vp]),
     "b200_ctx_logits_last_f32": (C.c_int, [_vp, _i32, _vp, _vp]),

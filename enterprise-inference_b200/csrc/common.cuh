@@ -267,15 +267,16 @@ int embed_scaled(const int32_t* ids, const __nv_bfloat16* table, float* out, int
 int layernorm_stream(bool f32, float* x, const void* y, const float* yparts, int n_parts, const float* w_post,
                      const float* w_next, void* out, const int32_t* rows, int T, int width, float eps, cudaStream_t s);
 // whole-projection RMS norm of q and k, interleaved partial rotation from a cos|sin table, unit-RMS (optionally rotated)
-// values, k/v into the paged cache
+// values, k/v into the paged cache (rows of kstride / vstride elements, 0: dim / vdim; a wider row's tail is zeroed, and
+// bf16 queries in qout16 get rows of kstride elements too)
 int qk_norm_rotate_cache(bool f32, const void* qkv, const float* qw, const float* kw, const int32_t* positions,
                          const int32_t* slots, const float* rot, int rot_dims, const float* vrot, float* qout, void* kc,
                          void* vc, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float eps,
-                         int64_t max_pos, cudaStream_t s, __nv_bfloat16* qout16 = nullptr);
+                         int64_t max_pos, cudaStream_t s, __nv_bfloat16* qout16 = nullptr, int kstride = 0, int vstride = 0);
 // attention output rows turned back by their position (bf16, in place): the closing step of rotated values when the
 // attention kernel itself does not do it
-int rotate_back_rows(__nv_bfloat16* a, const int32_t* positions, const float* vrot, int T, int heads, int vdim, int64_t max_pos,
-                     cudaStream_t s);
+int rotate_back_rows(const __nv_bfloat16* in, int in_stride, __nv_bfloat16* out, const int32_t* positions, const float* vrot, int T,
+                     int heads, int vdim, int64_t max_pos, cudaStream_t s);
 int convert_f32_to_bf16(const float* in, __nv_bfloat16* out, int64_t n, cudaStream_t s);
 int convert_bf16_to_f32(const __nv_bfloat16* in, float* out, int64_t n, cudaStream_t s);
 // paged softmax attention for any head sizes (attn_anydim.cu)

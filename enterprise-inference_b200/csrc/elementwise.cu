@@ -341,30 +341,62 @@ template <typename AT> __device__ __forceinline__ void act_store(AT* p, int64_t 
 template <> __device__ __forceinline__ void act_store<float>(float* p, int64_t i, float v) { p[i] = v; }
 template <> __device__ __forceinline__ void act_store<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
-template <typename AT>
+// four consecutive activations (width % 4 == 0, 16-byte aligned fp32 rows / 8-byte aligned bf16 rows)
+template <typename AT> __device__ __forceinline__ float4 act_load4(const AT* p, int64_t i);
+template <> __device__ __forceinline__ float4 act_load4<float>(const float* p, int64_t i) { return *reinterpret_cast<const float4*>(p + i); }
+template <> __device__ __forceinline__ float4 act_load4<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p + i);
+  return make_float4(bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y));
+}
+template <typename AT> __device__ __forceinline__ void act_store4(AT* p, int64_t i, float4 v);
+template <> __device__ __forceinline__ void act_store4<float>(float* p, int64_t i, float4 v) { *reinterpret_cast<float4*>(p + i) = v; }
+template <> __device__ __forceinline__ void act_store4<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float4 v) {
+  *reinterpret_cast<uint2*>(p + i) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+}
+
+// VEC = 4: width % 4 == 0, every access is 4 elements wide; VEC = 1: any width.  The order of every sum over the row is the
+// same function of (width, VEC) for every row, so a row's result does not depend on the step it is part of.
+template <typename AT, int VEC>
 __global__ void __launch_bounds__(kLnThreads)
 layernorm_stream_kernel(float* x, const AT* __restrict__ y, const float* __restrict__ yparts, int n_parts,
                         const float* __restrict__ w_post, const float* __restrict__ w_next, AT* __restrict__ out,
                         const int32_t* __restrict__ rows, int width, float eps) {
-  extern __shared__ float ln_row[];
+  extern __shared__ __align__(16) float ln_row[];
   __shared__ float red[kLnThreads / 32];
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
-  const int64_t xr = (int64_t)(rows ? rows[t] : t) * width;
+  const int64_t xrow = rows ? rows[t] : t;
+  const int64_t xr = xrow * width;
   const float inv_w = 1.0f / (float)width;
+  const int step = blockDim.x * VEC;
   if (y != nullptr || yparts != nullptr) {
     float sum = 0.f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      float v;
-      if (y != nullptr) {
-        v = act_load<AT>(y, xr + c);
+    for (int c = threadIdx.x * VEC; c < width; c += step) {
+      if constexpr (VEC == 4) {
+        float4 v;
+        if (y != nullptr) {
+          v = act_load4<AT>(y, xr + c);
+        } else {
+          v = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int p = 0; p < n_parts; ++p) {
+            const float4 q = *reinterpret_cast<const float4*>(yparts + (xrow * n_parts + p) * width + c);
+            v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+          }
+        }
+        *reinterpret_cast<float4*>(ln_row + c) = v;
+        sum += (v.x + v.y) + (v.z + v.w);
       } else {
-        v = 0.f;
-        for (int p = 0; p < n_parts; ++p) v += yparts[((int64_t)(rows ? rows[t] : t) * n_parts + p) * width + c];
+        float v;
+        if (y != nullptr) {
+          v = act_load<AT>(y, xr + c);
+        } else {
+          v = 0.f;
+          for (int p = 0; p < n_parts; ++p) v += yparts[(xrow * n_parts + p) * width + c];
+        }
+        ln_row[c] = v;
+        sum += v;
       }
-      ln_row[c] = v;
-      sum += v;
     }
     const float mean = block_sum(sum, red) * inv_w;
     float sq = 0.f;
@@ -373,15 +405,28 @@ layernorm_stream_kernel(float* x, const AT* __restrict__ y, const float* __restr
       sq = fmaf(d, d, sq);
     }
     const float rstd = 1.0f / sqrtf(block_sum(sq, red) * inv_w + eps);
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      const float v = x[xr + c] + (ln_row[c] - mean) * rstd * w_post[c];
-      x[xr + c] = v;
-      ln_row[c] = v;
+    for (int c = threadIdx.x * VEC; c < width; c += step) {
+      if constexpr (VEC == 4) {
+        const float4 xo = *reinterpret_cast<const float4*>(x + xr + c), wv = *reinterpret_cast<const float4*>(w_post + c);
+        const float4 l = *reinterpret_cast<const float4*>(ln_row + c);
+        const float4 v = make_float4(xo.x + (l.x - mean) * rstd * wv.x, xo.y + (l.y - mean) * rstd * wv.y,
+                                     xo.z + (l.z - mean) * rstd * wv.z, xo.w + (l.w - mean) * rstd * wv.w);
+        *reinterpret_cast<float4*>(x + xr + c) = v;
+        *reinterpret_cast<float4*>(ln_row + c) = v;
+      } else {
+        const float v = x[xr + c] + (ln_row[c] - mean) * rstd * w_post[c];
+        x[xr + c] = v;
+        ln_row[c] = v;
+      }
     }
   } else {
-    for (int c = threadIdx.x; c < width; c += blockDim.x) ln_row[c] = x[xr + c];
+    for (int c = threadIdx.x * VEC; c < width; c += step) {
+      if constexpr (VEC == 4) *reinterpret_cast<float4*>(ln_row + c) = *reinterpret_cast<const float4*>(x + xr + c);
+      else ln_row[c] = x[xr + c];
+    }
   }
   if (w_next == nullptr) return;
+  __syncthreads();   // the sums below read elements other threads staged
   float sum = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) sum += ln_row[c];
   const float mean = block_sum(sum, red) * inv_w;
@@ -391,8 +436,15 @@ layernorm_stream_kernel(float* x, const AT* __restrict__ y, const float* __restr
     sq = fmaf(d, d, sq);
   }
   const float rstd = 1.0f / sqrtf(block_sum(sq, red) * inv_w + eps);
-  for (int c = threadIdx.x; c < width; c += blockDim.x)
-    act_store<AT>(out, (int64_t)t * width + c, (ln_row[c] - mean) * rstd * w_next[c]);
+  for (int c = threadIdx.x * VEC; c < width; c += step) {
+    if constexpr (VEC == 4) {
+      const float4 l = *reinterpret_cast<const float4*>(ln_row + c), wv = *reinterpret_cast<const float4*>(w_next + c);
+      act_store4<AT>(out, (int64_t)t * width + c, make_float4((l.x - mean) * rstd * wv.x, (l.y - mean) * rstd * wv.y,
+                                                                (l.z - mean) * rstd * wv.z, (l.w - mean) * rstd * wv.w));
+    } else {
+      act_store<AT>(out, (int64_t)t * width + c, (ln_row[c] - mean) * rstd * w_next[c]);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -409,7 +461,7 @@ qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict_
                             const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
                             const float* __restrict__ rot, int rot_dims, const float* __restrict__ vrot,
                             float* __restrict__ qout, __nv_bfloat16* __restrict__ qout16, CT* kc, CT* vc, int heads, int kv_heads,
-                            int dim, int vdim, int block_size, float eps, int64_t max_pos) {
+                            int dim, int vdim, int block_size, float eps, int64_t max_pos, int kstride, int vstride) {
   extern __shared__ float row[];
   __shared__ float red[8];
   pdl_wait();
@@ -460,15 +512,38 @@ qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict_
       v = (d & 1) ? fmaf(v, cs, o * sn) : fmaf(v, cs, -o * sn);
     }
     if (is_q) {
-      if (qout16) qout16[(int64_t)t * qn + e] = __float2bfloat16_rn(v);   // for the tensor-core attention kernels
+      // bf16 queries for the tensor-core attention kernels: heads as wide as the key cache's rows
+      if (qout16) qout16[((int64_t)t * heads + e / dim) * kstride + d] = __float2bfloat16_rn(v);
       else qout[(int64_t)t * qn + e] = v;
     } else if (slot >= 0) {
       const int g = e / dim;
-      if (sizeof(CT) == 4) reinterpret_cast<float*>(kc)[((blk * kv_heads + g) * block_size + off) * dim + d] = v;
-      else reinterpret_cast<__nv_bfloat16*>(kc)[((blk * kv_heads + g) * block_size + off) * dim + d] = __float2bfloat16_rn(v);
+      if (sizeof(CT) == 4) reinterpret_cast<float*>(kc)[((blk * kv_heads + g) * block_size + off) * kstride + d] = v;
+      else reinterpret_cast<__nv_bfloat16*>(kc)[((blk * kv_heads + g) * block_size + off) * kstride + d] = __float2bfloat16_rn(v);
     }
   }
+  // rows wider than the head (a cache laid out for 128-wide kernels): the tail is kept at zero, so that it adds nothing
+  // to a score and nothing to an output
+  if (kstride > dim) {
+    const int pad = kstride - dim;
+    if (qout16)
+      for (int c = threadIdx.x; c < heads * pad; c += blockDim.x)
+        qout16[((int64_t)t * heads + c / pad) * kstride + dim + c % pad] = __float2bfloat16_rn(0.f);
+    if (slot >= 0)
+      for (int c = threadIdx.x; c < kv_heads * pad; c += blockDim.x) {
+        const int64_t at = ((blk * kv_heads + c / pad) * block_size + off) * kstride + dim + c % pad;
+        if (sizeof(CT) == 4) reinterpret_cast<float*>(kc)[at] = 0.f;
+        else reinterpret_cast<__nv_bfloat16*>(kc)[at] = __float2bfloat16_rn(0.f);
+      }
+  }
   if (slot < 0) return;
+  if (vstride > vdim) {
+    const int pad = vstride - vdim;
+    for (int c = threadIdx.x; c < kv_heads * pad; c += blockDim.x) {
+      const int64_t at = ((blk * kv_heads + c / pad) * block_size + off) * vstride + vdim + c % pad;
+      if (sizeof(CT) == 4) reinterpret_cast<float*>(vc)[at] = 0.f;
+      else reinterpret_cast<__nv_bfloat16*>(vc)[at] = __float2bfloat16_rn(0.f);
+    }
+  }
   for (int c = threadIdx.x; c < vn; c += blockDim.x) {
     const int g = c / vdim, d = c % vdim;
     float v = row[qn + kn + c] * vr[g];
@@ -478,28 +553,31 @@ qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict_
       const float o = row[qn + kn + (c ^ 1)] * vr[g];
       v = (d & 1) ? fmaf(v, cs, o * sn) : fmaf(v, cs, -o * sn);
     }
-    if (sizeof(CT) == 4) reinterpret_cast<float*>(vc)[((blk * kv_heads + g) * block_size + off) * vdim + d] = v;
-    else reinterpret_cast<__nv_bfloat16*>(vc)[((blk * kv_heads + g) * block_size + off) * vdim + d] = __float2bfloat16_rn(v);
+    if (sizeof(CT) == 4) reinterpret_cast<float*>(vc)[((blk * kv_heads + g) * block_size + off) * vstride + d] = v;
+    else reinterpret_cast<__nv_bfloat16*>(vc)[((blk * kv_heads + g) * block_size + off) * vstride + d] = __float2bfloat16_rn(v);
   }
 }
 
 // Turns the rows of an attention output back by the query's position: pair (2m, 2m+1) of every head by -pos * f_m, from the
-// table the cache writer used ([pos][cos half | sin half] fp32).  In place, bf16, one thread per pair.
+// table the cache writer used ([pos][cos half | sin half] fp32; null: no rotation).  The input heads may be wider than vdim
+// (in_stride elements each, the output of kernels built for 128-wide heads); the output heads are packed.  bf16, one thread
+// per pair; in == out is allowed when the widths agree.
 __global__ void __launch_bounds__(256)
-rotate_back_rows_kernel(__nv_bfloat16* __restrict__ a, const int32_t* __restrict__ positions, const float* __restrict__ vrot,
-                        int heads, int vdim, int64_t max_pos) {
+rotate_back_rows_kernel(const __nv_bfloat16* in, int in_stride, __nv_bfloat16* out, const int32_t* __restrict__ positions,
+                        const float* __restrict__ vrot, int heads, int vdim, int64_t max_pos) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, vhalf = vdim >> 1;
   int pos = positions[t];
   pos = pos < 0 ? 0 : (pos >= max_pos ? (int)max_pos - 1 : pos);
-  const float* cs = vrot + (int64_t)pos * 2 * vhalf;
-  __nv_bfloat162* row = reinterpret_cast<__nv_bfloat162*>(a + (int64_t)t * heads * vdim);
+  const float* cs = vrot ? vrot + (int64_t)pos * 2 * vhalf : nullptr;
+  const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(in + (int64_t)t * heads * in_stride);
+  __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + (int64_t)t * heads * vdim);
   for (int i = threadIdx.x; i < heads * vhalf; i += 256) {
-    const int m = i % vhalf;
-    const float2 uv = __bfloat1622float2(row[i]);
-    const float c = cs[m], sn = cs[vhalf + m];
-    row[i] = __floats2bfloat162_rn(fmaf(uv.x, c, uv.y * sn), fmaf(uv.y, c, -uv.x * sn));
+    const int h = i / vhalf, m = i % vhalf;
+    const float2 uv = __bfloat1622float2(src[h * (in_stride >> 1) + m]);
+    const float c = cs ? cs[m] : 1.f, sn = cs ? cs[vhalf + m] : 0.f;
+    dst[i] = __floats2bfloat162_rn(fmaf(uv.x, c, uv.y * sn), fmaf(uv.y, c, -uv.x * sn));
   }
 }
 
@@ -578,9 +656,18 @@ static int layernorm_stream_t(float* x, const void* y, const float* yparts, int 
   if (T == 0) return B200_OK;
   const size_t smem = (size_t)width * 4;
   B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "layernorm: width %d too large", width);
+  const uintptr_t ptrs = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(yparts) |
+                         reinterpret_cast<uintptr_t>(w_post) | reinterpret_cast<uintptr_t>(w_next) | reinterpret_cast<uintptr_t>(out);
+  if (width % 4 == 0 && ptrs % 16 == 0) {
+    static bool done4[64] = {};
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(layernorm_stream_kernel<AT, 4>, 200 * 1024, done4));
+    B200_CUDA(launch(layernorm_stream_kernel<AT, 4>, dim3(T), dim3(kLnThreads), smem, s, x, (const AT*)y, yparts, n_parts, w_post,
+                     w_next, (AT*)out, rows, width, eps));
+    return B200_OK;
+  }
   static bool done[64] = {};
-  if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(layernorm_stream_kernel<AT>, 200 * 1024, done));
-  B200_CUDA(launch(layernorm_stream_kernel<AT>, dim3(T), dim3(kLnThreads), smem, s, x, (const AT*)y, yparts, n_parts, w_post,
+  if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(layernorm_stream_kernel<AT, 1>, 200 * 1024, done));
+  B200_CUDA(launch(layernorm_stream_kernel<AT, 1>, dim3(T), dim3(kLnThreads), smem, s, x, (const AT*)y, yparts, n_parts, w_post,
                    w_next, (AT*)out, rows, width, eps));
   return B200_OK;
 }
@@ -595,8 +682,11 @@ int layernorm_stream(bool f32, float* x, const void* y, const float* yparts, int
 int qk_norm_rotate_cache(bool f32, const void* qkv, const float* qw, const float* kw, const int32_t* positions,
                          const int32_t* slots, const float* rot, int rot_dims, const float* vrot, float* qout, void* kc,
                          void* vc, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float eps,
-                         int64_t max_pos, cudaStream_t s, __nv_bfloat16* qout16) {
+                         int64_t max_pos, cudaStream_t s, __nv_bfloat16* qout16, int kstride, int vstride) {
   if (T == 0) return B200_OK;
+  if (kstride <= 0) kstride = dim;
+  if (vstride <= 0) vstride = vdim;
+  B200_REQUIRE(kstride >= dim && vstride >= vdim, B200_ERR_INVALID, "rotation: cache rows narrower than the heads");
   B200_REQUIRE(!(f32 && qout16), B200_ERR_INVALID, "rotation: bf16 queries are for the bf16 mode");
   B200_REQUIRE(dim % 2 == 0 && rot_dims % 2 == 0 && rot_dims <= dim && (vrot == nullptr || vdim % 2 == 0), B200_ERR_UNSUPPORTED,
                "rotation: head sizes must be even (dim %d, rot_dims %d, vdim %d)", dim, rot_dims, vdim);
@@ -606,22 +696,24 @@ int qk_norm_rotate_cache(bool f32, const void* qkv, const float* qw, const float
   if (f32) {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(qk_norm_rotate_cache_kernel<float, float>, 200 * 1024, done[0]));
     B200_CUDA(launch(qk_norm_rotate_cache_kernel<float, float>, dim3(T), dim3(256), smem, s, (const float*)qkv, qw, kw, positions,
-                     slots, rot, rot_dims, vrot, qout, (__nv_bfloat16*)nullptr, (float*)kc, (float*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos));
+                     slots, rot, rot_dims, vrot, qout, (__nv_bfloat16*)nullptr, (float*)kc, (float*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos, kstride, vstride));
   } else {
     if (smem > 48 * 1024)
       B200_CUDA(ensure_dynamic_smem(qk_norm_rotate_cache_kernel<__nv_bfloat16, __nv_bfloat16>, 200 * 1024, done[1]));
     B200_CUDA(launch(qk_norm_rotate_cache_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), smem, s,
                      (const __nv_bfloat16*)qkv, qw, kw, positions, slots, rot, rot_dims, vrot, qout, qout16, (__nv_bfloat16*)kc,
-                     (__nv_bfloat16*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos));
+                     (__nv_bfloat16*)vc, heads, kv_heads, dim, vdim, block_size, eps, max_pos, kstride, vstride));
   }
   return B200_OK;
 }
 
-int rotate_back_rows(__nv_bfloat16* a, const int32_t* positions, const float* vrot, int T, int heads, int vdim, int64_t max_pos,
-                     cudaStream_t s) {
-  B200_REQUIRE(vdim % 2 == 0 && reinterpret_cast<uintptr_t>(a) % 4 == 0, B200_ERR_UNSUPPORTED, "rotate_back: vdim %d must be even", vdim);
+int rotate_back_rows(const __nv_bfloat16* in, int in_stride, __nv_bfloat16* out, const int32_t* positions, const float* vrot, int T,
+                     int heads, int vdim, int64_t max_pos, cudaStream_t s) {
+  B200_REQUIRE(vdim % 2 == 0 && in_stride % 2 == 0 && in_stride >= vdim &&
+                   ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 3) == 0 && (in != out || in_stride == vdim),
+               B200_ERR_UNSUPPORTED, "rotate_back: vdim %d in rows of %d", vdim, in_stride);
   if (T == 0) return B200_OK;
-  B200_CUDA(launch(rotate_back_rows_kernel, dim3(T), dim3(256), (size_t)0, s, a, positions, vrot, heads, vdim, max_pos));
+  B200_CUDA(launch(rotate_back_rows_kernel, dim3(T), dim3(256), (size_t)0, s, in, in_stride, out, positions, vrot, heads, vdim, max_pos));
   return B200_OK;
 }
 

@@ -46,6 +46,7 @@ struct StackModel {
   int32_t* route_ids = nullptr;
   float *route_w = nullptr, *parts = nullptr, *route_logits = nullptr;
   void *attn_ws = nullptr, *moe_ws = nullptr;
+  void* attn_wide = nullptr;    // [T][heads][128] bf16: what the 128-wide attention kernels write for narrower value heads
   void* attn_tc_ws = nullptr;   // row plan and split partials of the 128-wide tensor-core attention kernels
   int64_t attn_tc_ws_bytes = 0;
   float* tap = nullptr;
@@ -53,13 +54,17 @@ struct StackModel {
 
 bool paged_attn_tc_supported(int hq, int hkv, int block_size);   // attn_tc.cu
 
-// bf16 mode, 128-wide keys and values in blocks of 128 tokens: the tcgen05 attention kernels of the fixed decoder stack
-// serve the layer (bf16 queries, the output rotation as a step of its own); every other shape takes attn_anydim.cu
+// bf16 mode, keys and values of 64 to 128 dimensions in blocks of 128 tokens: the tcgen05 attention kernels of the fixed
+// decoder stack serve the layer.  They are built for 128-wide heads, so the layer's cache rows and its bf16 queries are
+// 128 wide with a zero tail (which adds nothing to a score, and whose outputs are dropped); the output rotation and the
+// packing of narrower value heads are a step of their own.  Every other shape takes attn_anydim.cu.
 static bool layer_attn_tc(const b200_stack_cfg& m, const b200_stack_layer& L) {
   static const int env = getenv("B200_STACK_ATTN_TC") ? atoi(getenv("B200_STACK_ATTN_TC")) : 1;
-  return env && !m.f32 && L.dim == kHeadDim && L.vdim == kHeadDim && L.scale > 0.f &&
-         paged_attn_tc_supported(L.heads, L.kv_heads, m.block_size);
+  return env && !m.f32 && L.dim >= kHeadDim / 2 && L.dim <= kHeadDim && L.vdim >= kHeadDim / 2 && L.vdim <= kHeadDim &&
+         L.scale > 0.f && paged_attn_tc_supported(L.heads, L.kv_heads, m.block_size);
 }
+static int cache_kdim(const b200_stack_cfg& m, const b200_stack_layer& L) { return layer_attn_tc(m, L) ? kHeadDim : L.dim; }
+static int cache_vdim(const b200_stack_cfg& m, const b200_stack_layer& L) { return layer_attn_tc(m, L) ? kHeadDim : L.vdim; }
 
 static int64_t up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
@@ -139,7 +144,8 @@ int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
     if (layer_attn_tc(m, L)) {
       __nv_bfloat16* q16 = reinterpret_cast<__nv_bfloat16*>(M->q);
       STEP(qk_norm_rotate_cache(f32, M->qkv, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, vrot, nullptr, W.kc, W.vc, T,
-                                L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, max_pos, s, q16));
+                                L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, max_pos, s, q16, kHeadDim, kHeadDim));
+      __nv_bfloat16* wide = L.vdim == kHeadDim ? (__nv_bfloat16*)M->attn : (__nv_bfloat16*)M->attn_wide;
       int pack = attn_pack;
       if (pack > 0) {
         const int G = L.heads / L.kv_heads;
@@ -151,10 +157,11 @@ int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
         }
         pack = pack_group == G ? 2 : 1;
       }
-      STEP(paged_attn_ex(q16, L.heads * L.dim, (const __nv_bfloat16*)W.kc, (const __nv_bfloat16*)W.vc, a.block_table, a.bt_stride,
-                         a.row_to_seq, a.ctx_lens, (__nv_bfloat16*)M->attn, L.heads * L.vdim, T, L.heads, L.kv_heads, m.block_size,
-                         a.max_ctx, L.scale, M->attn_tc_ws, M->attn_tc_ws_bytes, pack, s));
-      if (vrot) STEP(rotate_back_rows((__nv_bfloat16*)M->attn, a.positions, vrot, T, L.heads, L.vdim, max_pos, s));
+      STEP(paged_attn_ex(q16, L.heads * kHeadDim, (const __nv_bfloat16*)W.kc, (const __nv_bfloat16*)W.vc, a.block_table, a.bt_stride,
+                         a.row_to_seq, a.ctx_lens, wide, L.heads * kHeadDim, T, L.heads, L.kv_heads, m.block_size, a.max_ctx,
+                         L.scale, M->attn_tc_ws, M->attn_tc_ws_bytes, pack, s));
+      if (vrot || L.vdim != kHeadDim)
+        STEP(rotate_back_rows(wide, kHeadDim, (__nv_bfloat16*)M->attn, a.positions, vrot, T, L.heads, L.vdim, max_pos, s));
     } else {
       STEP(qk_norm_rotate_cache(f32, M->qkv, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, vrot, M->q, W.kc, W.vc, T,
                                 L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, max_pos, s));
@@ -283,7 +290,10 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
   const int64_t attn_ws_bytes = paged_attn_anydim_workspace_bytes((int)T);
   int tc_heads = 0;
   for (int l = 0; l < cfg->n_layers; ++l)
-    if (layer_attn_tc(*cfg, layers[l])) tc_heads = std::max(tc_heads, layers[l].heads);
+    if (layer_attn_tc(*cfg, layers[l])) {
+      tc_heads = std::max(tc_heads, layers[l].heads);
+      max_q = std::max(max_q, layers[l].heads * kHeadDim / 2);   // bf16 queries of 128 in the fp32 query buffer
+    }
   M->attn_tc_ws_bytes = 16;
   if (tc_heads) {
     int max_ctx = 128;   // graph replay rounds a step's longest context up to a power of two
@@ -312,6 +322,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&M->attn_ws, attn_ws_bytes},
       {(void**)&M->moe_ws, moe_ws_bytes},
       {(void**)&M->attn_tc_ws, M->attn_tc_ws_bytes},
+      {(void**)&M->attn_wide, tc_heads ? T * tc_heads * kHeadDim * 2 : 16},
       {(void**)&c->logits, R * (int64_t)c->logits_ld * 2},
       {(void**)&c->logits_f32, cfg->f32 ? R * (int64_t)c->logits_ld * 4 : 16},
       {(void**)&c->lin_ws, c->lin_ws_bytes},
@@ -402,6 +413,15 @@ extern "C" int b200_stack_set_kv_cache(b200_ctx* c, int32_t layer, void* k_cache
   c->n_blocks = n_blocks;
   M->w[layer].kc = k_cache;
   M->w[layer].vc = v_cache;
+  return B200_OK;
+}
+
+extern "C" int b200_stack_cache_dims(b200_ctx* c, int32_t layer, int32_t* k_dim, int32_t* v_dim) {
+  B200_REQUIRE(c && c->stack && k_dim && v_dim, B200_ERR_INVALID, "stack_cache_dims: bad argument");
+  StackModel* M = c->stack;
+  B200_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, B200_ERR_INVALID, "stack_cache_dims: layer %d out of range", layer);
+  *k_dim = cache_kdim(M->cfg, M->layers[layer]);
+  *v_dim = cache_vdim(M->cfg, M->layers[layer]);
   return B200_OK;
 }
 

@@ -444,8 +444,13 @@ class StackRunner(ModelRunner):
         for i, t in enumerate(self._tables):
             _abi.check(self.lib.b200_stack_set_rot_table(self.ctx, i, t.data_ptr(), t.shape[0], t.shape[2]))
 
-        # paged caches, one pair per layer: [n_blocks][kv_heads][block][dim | vdim], zero-filled
-        per_block = cfg.kv_bytes_per_token(self.f32) * block_size
+        # paged caches, one pair per layer: [n_blocks][kv_heads][block][row widths the ctx names], zero-filled
+        self.cache_dims = []
+        for i in range(len(cfg.layers)):
+            kd, vd = C.c_int32(), C.c_int32()
+            _abi.check(self.lib.b200_stack_cache_dims(self.ctx, i, C.byref(kd), C.byref(vd)))
+            self.cache_dims.append((kd.value, vd.value))
+        per_block = sum(L.mixer.kv_heads * (kd + vd) for L, (kd, vd) in zip(cfg.layers, self.cache_dims)) * (4 if self.f32 else 2) * block_size
         if n_blocks is None:
             if kv_cache_gib is None:
                 free, _ = torch.cuda.mem_get_info(self.device)
@@ -456,8 +461,8 @@ class StackRunner(ModelRunner):
         self.k_cache, self.v_cache = [], []
         for i, L in enumerate(cfg.layers):
             a = L.mixer
-            k = torch.zeros((n_blocks, a.kv_heads, block_size, a.dim), dtype=cdt, device=self.device)
-            v = torch.zeros((n_blocks, a.kv_heads, block_size, a.vdim), dtype=cdt, device=self.device)
+            k = torch.zeros((n_blocks, a.kv_heads, block_size, self.cache_dims[i][0]), dtype=cdt, device=self.device)
+            v = torch.zeros((n_blocks, a.kv_heads, block_size, self.cache_dims[i][1]), dtype=cdt, device=self.device)
             self.k_cache.append(k)
             self.v_cache.append(v)
             _abi.check(self.lib.b200_stack_set_kv_cache(self.ctx, i, k.data_ptr(), v.data_ptr(), n_blocks))

@@ -411,8 +411,11 @@ typedef enum b200_stack_weight {
 B200_API int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_layer* layers, b200_ctx** out);
 /* Pointers are borrowed for the life of the ctx; rows/cols are checked ([rows][cols], vectors as [n][1]). */
 B200_API int b200_stack_set_weight(b200_ctx* ctx, int32_t layer, int32_t kind, const void* w, int64_t rows, int64_t cols);
-/* Paged cache of one layer, caller-owned: k [n_blocks][kv_heads][block_size][dim], v [...][vdim]; bf16, or fp32 when the
- * ctx was created with f32.  Every layer gets the same n_blocks (one block table serves all layers). */
+/* Row widths of one layer's cache: dim and vdim, or 128 for both where the layer runs on the attention kernels built for
+ * 128-wide heads (bf16, blocks of 128 tokens, dim and vdim in [64, 128]); the tail of such rows is kept at zero. */
+B200_API int b200_stack_cache_dims(b200_ctx* ctx, int32_t layer, int32_t* k_dim, int32_t* v_dim);
+/* Paged cache of one layer, caller-owned: k [n_blocks][kv_heads][block_size][k_dim], v [...][v_dim] (b200_stack_cache_dims);
+ * bf16, or fp32 when the ctx was created with f32.  Every layer gets the same n_blocks (one block table serves all layers). */
 B200_API int b200_stack_set_kv_cache(b200_ctx* ctx, int32_t layer, void* k_cache, void* v_cache, int64_t n_blocks);
 /* cos|sin table `index` (0..15): fp32 [n_pos][2][half] (the cos row of a position, then its sin row). */
 B200_API int b200_stack_set_rot_table(b200_ctx* ctx, int32_t index, const float* table, int64_t n_pos, int32_t half);

@@ -371,12 +371,15 @@ def test_bf16_mode_within_bf16_noise_and_equal_across_schedules(model_a):
 WIDE = dict(width=128, vocab=160, scale=1.5, eps=1e-5, layers=[
     U.layer(heads=4, kv_heads=1, dim=128, vdim=128, rot_dims=64, att_scale=0.09, moe=dict(experts=8, top=2, groups=2, keep=1, ff=64)),
     U.layer(heads=2, kv_heads=2, dim=128, vdim=128, rot_dims=128, scaling=None, att_scale=0.12, moe=None),
-    U.layer(heads=4, kv_heads=2, dim=64, vdim=128, rot_dims=32, att_scale=0.12, moe=dict(experts=4, top=1, groups=1, keep=1, ff=72))])
+    U.layer(heads=4, kv_heads=2, dim=64, vdim=96, rot_dims=32, att_scale=0.12, moe=dict(experts=4, top=2, groups=1, keep=1, ff=72)),
+    U.layer(heads=2, kv_heads=1, dim=80, vdim=128, rot_dims=80, att_scale=0.11, moe=None),
+    U.layer(heads=2, kv_heads=1, dim=128, vdim=32, rot_dims=8, att_scale=0.09, moe=None)])
 
 
 def test_128_wide_heads_take_the_tensor_core_attention_and_agree_with_the_generic_kernels():
-    """bf16 mode with blocks of 128 tokens: layers with 128-wide keys and values run the tcgen05 attention kernels (two group
-    sizes in one model, so the row plan is rebuilt between layers), the third layer keeps the generic kernels.  Against the
+    """bf16 mode with blocks of 128 tokens: layers with keys and values of 64 to 128 dimensions run the tcgen05 attention
+    kernels (several group sizes in one model, so the row plan is rebuilt between layers; narrower heads sit in 128-wide
+    cache rows with a zero tail), the last layer (32-wide values) keeps the generic kernels.  Against the
     oracle within bf16 noise, against the same model in blocks of 16 (generic kernels everywhere), and across schedules:
     keys beyond one and two blocks, portions that end at and next to a block border, decoding over a border."""
     cfg = U.make_cfg(**WIDE)
@@ -394,11 +397,11 @@ def test_128_wide_heads_take_the_tensor_core_attention_and_agree_with_the_generi
     small = U.replay(U.make_engine(r16), [[("a", 300)], [("b", 131)], [("c", 40)]], prompts)
     r16.close()
     for n in prompts:
-        e = U.rel_rms(whole[n], want[n])
-        assert np.median(e) < 0.03 and (e < 0.1).mean() > 0.9, (n, float(np.median(e)), float(e.max()))
+        e = U.rel_rms(whole[n], want[n])      # five layers of bf16 rounding; a wrong key, row or rotation gives errors near 1
+        assert np.median(e) < 0.05 and (e < 0.15).mean() > 0.9, (n, float(np.median(e)), float(e.max()))
         for other in (mixed, small):
             d = U.rel_rms(other[n], whole[n])
-            assert np.median(d) < 0.03 and (d < 0.1).mean() > 0.9, (n, float(np.median(d)), float(d.max()))
+            assert np.median(d) < 0.05 and (d < 0.15).mean() > 0.9, (n, float(np.median(d)), float(d.max()))
 
 
 def test_greedy_generation_through_the_engines_own_scheduler(model_odd, tmp_path):
