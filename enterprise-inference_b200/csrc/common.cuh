@@ -202,6 +202,8 @@ int linear_tc_grouped_tile(int pairs, int experts);
 int linear_tc_grouped(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, const __nv_bfloat16* w, int experts, int n_out, int k,
                       const int32_t* tile_expert, __nv_bfloat16* y, int64_t ldy, const int32_t* row_pair, const float* wts,
                       float* out, cudaStream_t s);
+int linear_tc_grouped_gate_up(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, const __nv_bfloat16* w, int experts, int ff,
+                              int k, const int32_t* tile_expert, __nv_bfloat16* y, cudaStream_t s);
 int rmsnorm(const __nv_bfloat16* x, __nv_bfloat16* res, const __nv_bfloat16* w, __nv_bfloat16* y, int T,
             int hidden, float eps, cudaStream_t s);
 // fp32 residual stream (RMSNorm folded into the linears): embedding rows -> sres/ssq; stream rows -> normed bf16

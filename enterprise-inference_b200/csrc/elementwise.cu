@@ -470,11 +470,31 @@ qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict_
   const int qn = heads * dim, kn = kv_heads * dim, vn = kv_heads * vdim, rw = qn + kn + vn;
   float* vr = row + rw;   // per kv head: 1 / rms of the value
   float sq = 0.f, sk = 0.f;
-  for (int c = threadIdx.x; c < rw; c += blockDim.x) {
-    const float v = act_load<AT>(qkv, (int64_t)t * rw + c);
-    row[c] = v;
-    if (c < qn) sq = fmaf(v, v, sq);
-    else if (c < qn + kn) sk = fmaf(v, v, sk);
+  const bool pairs = (vdim & 1) == 0;   // dim is even by contract: with an even vdim every row splits into aligned pairs
+  if (pairs) {
+    for (int c = threadIdx.x * 2; c < rw; c += blockDim.x * 2) {
+      float v0, v1;
+      if (sizeof(AT) == 4) {
+        const float2 f = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(qkv) + (int64_t)t * rw + c);
+        v0 = f.x;
+        v1 = f.y;
+      } else {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(qkv) + (int64_t)t * rw + c));
+        v0 = f.x;
+        v1 = f.y;
+      }
+      row[c] = v0;
+      row[c + 1] = v1;
+      if (c < qn) sq = fmaf(v1, v1, fmaf(v0, v0, sq));
+      else if (c < qn + kn) sk = fmaf(v1, v1, fmaf(v0, v0, sk));
+    }
+  } else {
+    for (int c = threadIdx.x; c < rw; c += blockDim.x) {
+      const float v = act_load<AT>(qkv, (int64_t)t * rw + c);
+      row[c] = v;
+      if (c < qn) sq = fmaf(v, v, sq);
+      else if (c < qn + kn) sk = fmaf(v, v, sk);
+    }
   }
   const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)qn + eps);
   const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)kn + eps);
@@ -498,27 +518,29 @@ qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict_
   const float* rc = rot ? rot + (int64_t)pos * rot_dims : nullptr;        // cos[half] | sin[half]
   const float* vcs = vrot ? vrot + (int64_t)pos * 2 * vhalf : nullptr;
   const int64_t blk = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot % block_size : 0;
-  for (int c = threadIdx.x; c < qn + kn; c += blockDim.x) {
+  for (int c = threadIdx.x * 2; c < qn + kn; c += blockDim.x * 2) {   // pair (c, c + 1): dim and the bases are even
     const bool is_q = c < qn;
     const int e = is_q ? c : c - qn;
     const int d = e % dim;
     const float r = is_q ? rq : rk;
     const float* w = is_q ? qw : kw;
-    float v = row[c] * r * w[e];
+    float v0 = row[c] * r * w[e], v1 = row[c + 1] * r * w[e + 1];
     if (d < rot_dims && rc) {
       const int i = d >> 1;
       const float cs = rc[i], sn = rc[half + i];
-      const float o = row[c ^ 1] * r * w[e ^ 1];   // partner of the pair (dim and the bases are even: c ^ 1 stays in the head)
-      v = (d & 1) ? fmaf(v, cs, o * sn) : fmaf(v, cs, -o * sn);
+      const float o0 = fmaf(v0, cs, -v1 * sn), o1 = fmaf(v1, cs, v0 * sn);
+      v0 = o0;
+      v1 = o1;
     }
     if (is_q) {
       // bf16 queries for the tensor-core attention kernels: heads as wide as the key cache's rows
-      if (qout16) qout16[((int64_t)t * heads + e / dim) * kstride + d] = __float2bfloat16_rn(v);
-      else qout[(int64_t)t * qn + e] = v;
+      if (qout16) *reinterpret_cast<__nv_bfloat162*>(qout16 + ((int64_t)t * heads + e / dim) * kstride + d) = __floats2bfloat162_rn(v0, v1);
+      else *reinterpret_cast<float2*>(qout + (int64_t)t * qn + e) = make_float2(v0, v1);
     } else if (slot >= 0) {
       const int g = e / dim;
-      if (sizeof(CT) == 4) reinterpret_cast<float*>(kc)[((blk * kv_heads + g) * block_size + off) * kstride + d] = v;
-      else reinterpret_cast<__nv_bfloat16*>(kc)[((blk * kv_heads + g) * block_size + off) * kstride + d] = __float2bfloat16_rn(v);
+      const int64_t at = ((blk * kv_heads + g) * block_size + off) * kstride + d;
+      if (sizeof(CT) == 4) *reinterpret_cast<float2*>(reinterpret_cast<float*>(kc) + at) = make_float2(v0, v1);
+      else *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(kc) + at) = __floats2bfloat162_rn(v0, v1);
     }
   }
   // rows wider than the head (a cache laid out for 128-wide kernels): the tail is kept at zero, so that it adds nothing
@@ -543,6 +565,23 @@ qk_norm_rotate_cache_kernel(const AT* __restrict__ qkv, const float* __restrict_
       if (sizeof(CT) == 4) reinterpret_cast<float*>(vc)[at] = 0.f;
       else reinterpret_cast<__nv_bfloat16*>(vc)[at] = __float2bfloat16_rn(0.f);
     }
+  }
+  if (pairs) {
+    for (int c = threadIdx.x * 2; c < vn; c += blockDim.x * 2) {
+      const int g = c / vdim, d = c % vdim;
+      float v0 = row[qn + kn + c] * vr[g], v1 = row[qn + kn + c + 1] * vr[g];
+      if (vcs) {
+        const int i = d >> 1;
+        const float cs = vcs[i], sn = vcs[vhalf + i];
+        const float o0 = fmaf(v0, cs, -v1 * sn), o1 = fmaf(v1, cs, v0 * sn);
+        v0 = o0;
+        v1 = o1;
+      }
+      const int64_t at = ((blk * kv_heads + g) * block_size + off) * vstride + d;
+      if (sizeof(CT) == 4) *reinterpret_cast<float2*>(reinterpret_cast<float*>(vc) + at) = make_float2(v0, v1);
+      else *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(vc) + at) = __floats2bfloat162_rn(v0, v1);
+    }
+    return;
   }
   for (int c = threadIdx.x; c < vn; c += blockDim.x) {
     const int g = c / vdim, d = c % vdim;

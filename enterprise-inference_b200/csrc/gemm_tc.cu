@@ -184,6 +184,9 @@ struct TcParams {
   // (-1: the tile is not in use and its CTAs leave at once).  The token rows are the experts' tokens, gathered so that
   // no tile holds rows of two experts.
   const int32_t* grp_tile;
+  // grouped gate|up with the SiLU*mul epilogue: an expert's rows are [gate (gu_ff) | up (gu_ff)]; slab m of the launch is
+  // gate rows m*64.. and the matching up rows, fetched as two 64-row boxes (the layout kSiluMul expects, made by TMA)
+  int gu_ff;
   // kScatter: row t of the launch goes to grp_out[grp_pair[t]][n_out] (fp32, unrounded) times grp_wt[grp_pair[t]];
   // grp_pair[t] < 0 marks a padding row
   // (both null: the identity and weight 1, i.e. a plain fp32 output)
@@ -448,7 +451,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     pdl_wait();
     const int e = __ldg(p.grp_tile + tok_tile);
     if (e < 0) return;   // whole CTA, before any barrier or TMEM allocation exists
-    w_row0 += e * p.n_out;
+    w_row0 = p.gu_ff ? e * 2 * p.gu_ff + m_tile * (kBlockM / 2) : w_row0 + e * p.n_out;
   }
 
   if (threadIdx.x == 0) {
@@ -491,7 +494,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       // weights first: they do not depend on the producer of x
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full[i], kTmaBytes);
-        tma_load_2d(smem + i * kStageBytes, &map_w, (kb0 + i) * kBlockK, w_row0, &full[i], w_policy);
+        if (p.gu_ff) {
+          tma_load_2d(smem + i * kStageBytes, &map_w, (kb0 + i) * kBlockK, w_row0, &full[i], w_policy);
+          tma_load_2d(smem + i * kStageBytes + kABytes / 2, &map_w, (kb0 + i) * kBlockK, w_row0 + p.gu_ff, &full[i], w_policy);
+        } else {
+          tma_load_2d(smem + i * kStageBytes, &map_w, (kb0 + i) * kBlockK, w_row0, &full[i], w_policy);
+        }
       }
       tc_trace(p, 1);   // W of the first stages requested
     }
@@ -512,7 +520,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       mbar_wait(&empty[st], ((i / S) - 1) & 1);
       if (issuer) {
         mbar_expect_tx(&full[st], kTmaBytes);
-        tma_load_2d(smem + st * kStageBytes, &map_w, (kb0 + i) * kBlockK, w_row0, &full[st], w_policy);
+        if (p.gu_ff) {
+          tma_load_2d(smem + st * kStageBytes, &map_w, (kb0 + i) * kBlockK, w_row0, &full[st], w_policy);
+          tma_load_2d(smem + st * kStageBytes + kABytes / 2, &map_w, (kb0 + i) * kBlockK, w_row0 + p.gu_ff, &full[st], w_policy);
+        } else {
+          tma_load_2d(smem + st * kStageBytes, &map_w, (kb0 + i) * kBlockK, w_row0, &full[st], w_policy);
+        }
         if constexpr (!NI)
           tma_load_2d(smem + st * kStageBytes + kABytes, &map_x, (kb0 + i) * kBlockK, tok_tile * N, &full[st], kEvictLast);
       }
@@ -1120,6 +1133,53 @@ int linear_tc_grouped_tile(int pairs, int experts) {
 }
 
 bool linear_tc_grouped_supported(int n_out, int k) { return n_out > 0 && k > 0 && k % 8 == 0; }
+
+// Gate|up of every expert with the SiLU*mul epilogue: w [experts][2 ff][k] (gate rows, then up rows), ff % 64 == 0;
+// y[row][ff] = bf16(silu(gate) * up).
+template <int N>
+static int launch_grouped_silu(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, const Plan& pl, cudaStream_t s) {
+  return launch_tc3<N, kSiluMul, stages_for(N), false>(mw, mx, p, pl, s);
+}
+
+int linear_tc_grouped_gate_up(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, const __nv_bfloat16* w, int experts, int ff,
+                              int k, const int32_t* tile_expert, __nv_bfloat16* y, cudaStream_t s) {
+  B200_REQUIRE(ff > 0 && ff % (kBlockM / 2) == 0 && k > 0 && k % 8 == 0, B200_ERR_UNSUPPORTED,
+               "linear_tc_grouped_gate_up: ff=%d must be a multiple of 64, k=%d of 8", ff, k);
+  B200_REQUIRE(x && w && y && tile_expert && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   ldx % 8 == 0,
+               B200_ERR_INVALID, "linear_tc_grouped_gate_up: operands must be 16-byte aligned");
+  B200_REQUIRE(N == 16 || N == 32 || N == 64 || N == 128, B200_ERR_INVALID, "linear_tc_grouped_gate_up: token tile %d", N);
+  B200_REQUIRE(n_tiles > 0 && n_tiles <= 65535 && experts > 0, B200_ERR_INVALID, "linear_tc_grouped_gate_up: %d tiles", n_tiles);
+  Plan pl;
+  pl.N = N;
+  pl.m_tiles = ff / (kBlockM / 2);
+  pl.tok_tiles = n_tiles;
+  pl.n_kblocks = (k + kBlockK - 1) / kBlockK;
+  pl.splits = 1;
+  pl.n_out_pad = pl.m_tiles * kBlockM;
+  TcParams p = {};
+  p.y = y;
+  p.ldy = ff;
+  p.T = n_tiles * N;
+  p.n_out = 2 * ff;
+  p.n_kblocks = pl.n_kblocks;
+  p.splits = 1;
+  p.n_out_pad = pl.n_out_pad;
+  p.grp_tile = tile_expert;
+  p.gu_ff = ff;
+  p.tile_n = N;
+  CUtensorMap mw, mx;
+  int rc = get_map(w, (uint64_t)experts * 2 * ff, (uint64_t)k, (uint64_t)k, kBlockM / 2, &mw);
+  if (rc) return rc;
+  rc = get_map(x, (uint64_t)n_tiles * N, (uint64_t)k, (uint64_t)ldx, (uint32_t)N, &mx);
+  if (rc) return rc;
+  switch (N) {
+    case 16: return launch_grouped_silu<16>(mw, mx, p, pl, s);
+    case 32: return launch_grouped_silu<32>(mw, mx, p, pl, s);
+    case 64: return launch_grouped_silu<64>(mw, mx, p, pl, s);
+    default: return launch_grouped_silu<128>(mw, mx, p, pl, s);
+  }
+}
 
 template <int N>
 static int launch_grouped(bool scatter, const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, const Plan& pl, cudaStream_t s) {

@@ -432,10 +432,18 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
                    tile_expert, row_pair));
   B200_CUDA(launch(moe_gather_kernel, dim3((unsigned)rows), dim3(128), (size_t)0, s, x, (const int32_t*)tile_expert,
                    (const int32_t*)row_pair, N, top, width, xg));
-  int rc = linear_tc_grouped(xg, width, N, n_tiles, w_gu, experts, 2 * ff, width, tile_expert, gu, 2 * ff, nullptr, nullptr, nullptr, s);
-  if (rc) return rc;
-  rc = silu_mul(gu, act, (int)rows, ff, s);
-  if (rc) return rc;
+  int rc;
+  static const int fuse_env = getenv("B200_MOE_FUSE_SILU") ? atoi(getenv("B200_MOE_FUSE_SILU")) : 1;
+  if (fuse_env && ff % 64 == 0) {
+    // gate and up rows of a slab come in as two 64-row boxes; the epilogue activates (as the dense gate|up linear does)
+    rc = linear_tc_grouped_gate_up(xg, width, N, n_tiles, w_gu, experts, ff, width, tile_expert, act, s);
+    if (rc) return rc;
+  } else {
+    rc = linear_tc_grouped(xg, width, N, n_tiles, w_gu, experts, 2 * ff, width, tile_expert, gu, 2 * ff, nullptr, nullptr, nullptr, s);
+    if (rc) return rc;
+    rc = silu_mul(gu, act, (int)rows, ff, s);
+    if (rc) return rc;
+  }
   return linear_tc_grouped(act, ff, N, n_tiles, w_down, experts, width, ff, tile_expert, nullptr, 0, row_pair, wts, parts, s);
 }
 
