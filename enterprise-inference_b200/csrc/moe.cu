@@ -318,52 +318,50 @@ moe_group_kernel(const int32_t* __restrict__ ids, int n_pairs, int experts, int 
                  int32_t* __restrict__ row_pair) {
   extern __shared__ int32_t gsm[];
   int32_t* cnt = gsm;                  // [experts]
-  int32_t* start = cnt + experts;      // [experts] first row of the expert's run
+  int32_t* start = cnt + experts;      // [experts] next free row of the expert's run
+  int32_t* chunk = start + experts;    // [kGroupChunk] the pair list, a chunk at a time
   pdl_wait();
   pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int e = threadIdx.x; e < experts; e += kGroupThreads) cnt[e] = 0;
   for (int i = threadIdx.x; i < n_tiles * N; i += kGroupThreads) row_pair[i] = -1;
   for (int i = threadIdx.x; i < n_tiles; i += kGroupThreads) tile_expert[i] = -1;
-  __syncthreads();
-  for (int i = threadIdx.x; i < n_pairs; i += kGroupThreads) {
-    const int e = ids[i];
-    if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < experts; ++e) {
-      const int nt = (cnt[e] + N - 1) / N;
-      start[e] = run * N;
-      for (int j = 0; j < nt && run + j < n_tiles; ++j) tile_expert[run + j] = e;
-      run += nt;
-    }
-  }
-  __syncthreads();
-  // the pair list goes through shared memory a chunk at a time: the walk below is a chain of ballots, and a global load
-  // inside it would pay its latency once per 32 pairs
-  int32_t* chunk = start + experts;   // [kGroupChunk]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c0 = 0; c0 < n_pairs; c0 += kGroupChunk) {
-    const int cn = min(kGroupChunk, n_pairs - c0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < cn; i += kGroupThreads) chunk[i] = ids[c0 + i];
-    __syncthreads();
-    for (int e = warp; e < experts; e += kGroupThreads / 32) {
-      if (cnt[e] == 0) continue;
-      int pos = start[e];
-      for (int b = 0; b < cn; b += 32) {
-        const int i = b + lane;
-        const bool mine = i < cn && chunk[i] == e;
-        const unsigned m = __ballot_sync(0xffffffffu, mine);
-        if (mine) {
-          const int r = pos + __popc(m & ((1u << lane) - 1u));
-          if (r < n_tiles * N) row_pair[r] = c0 + i;
+  // Two walks over the pair list, which goes through shared memory a chunk at a time (a global load inside the chain of
+  // ballots would pay its latency once per 32 pairs).  Warp w owns experts w, w + 32, ...: the first walk counts (no
+  // atomics: thousands of pairs on a few dozen counters serialise), the second one places.
+  for (int pass = 0; pass < 2; ++pass) {
+    for (int c0 = 0; c0 < n_pairs; c0 += kGroupChunk) {
+      const int cn = min(kGroupChunk, n_pairs - c0);
+      __syncthreads();
+      if (pass == 0 || n_pairs > kGroupChunk)
+        for (int i = threadIdx.x; i < cn; i += kGroupThreads) chunk[i] = ids[c0 + i];
+      __syncthreads();
+      for (int e = warp; e < experts; e += kGroupThreads / 32) {
+        if (pass == 1 && cnt[e] == 0) continue;
+        int pos = pass == 0 ? cnt[e] : start[e];
+        for (int b = 0; b < cn; b += 32) {
+          const int i = b + lane;
+          const bool mine = i < cn && chunk[i] == e;
+          const unsigned m = __ballot_sync(0xffffffffu, mine);
+          if (pass == 1 && mine) {
+            const int r = pos + __popc(m & ((1u << lane) - 1u));
+            if (r < n_tiles * N) row_pair[r] = c0 + i;
+          }
+          pos += __popc(m);
         }
-        pos += __popc(m);
+        __syncwarp();
+        if (lane == 0) (pass == 0 ? cnt : start)[e] = pos;   // this warp alone owns expert e
       }
-      __syncwarp();
-      if (lane == 0) start[e] = pos;   // this warp alone owns expert e
+    }
+    __syncthreads();
+    if (pass == 0 && threadIdx.x == 0) {
+      int run = 0;
+      for (int e = 0; e < experts; ++e) {
+        const int nt = (cnt[e] + N - 1) / N;
+        start[e] = run * N;
+        for (int j = 0; j < nt && run + j < n_tiles; ++j) tile_expert[run + j] = e;
+        run += nt;
+      }
     }
   }
 }

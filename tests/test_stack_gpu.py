@@ -251,9 +251,11 @@ def _experts_rounded(x, ids, wts, gate, up, down):
 
 
 @pytest.mark.parametrize("T,W,ff,experts,top", [(1, 64, 64, 8, 2), (3, 136, 72, 5, 5), (40, 64, 200, 4, 2), (300, 256, 136, 6, 3),
-                                                (700, 128, 64, 3, 1)])
+                                                (700, 128, 64, 3, 1), (3000, 64, 64, 4, 3)])
 def test_experts_tensor_core_form(T, W, ff, experts, top):
-    """Every token-tile size, runs that end inside a tile, experts nobody chose, slab rows past an expert's last row."""
+    """Every token-tile size, runs that end inside a tile, experts nobody chose, slab rows past an expert's last row, ff
+    that is and is not a multiple of 64 (activation in the epilogue or as a step of its own), more pairs than the grouping
+    kernel holds in shared memory at a time."""
     g = torch.Generator().manual_seed(T + W)
     x = torch.randn(T, W, generator=g).to(torch.bfloat16)
     gate = [U.bf16_exact(torch.randn(ff, W, generator=g) * W ** -0.5) for _ in range(experts)]
