@@ -307,62 +307,75 @@ moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restr
 
 
 // ---- tensor-core form: grouping and gather --------------------------------------------------------------------------------
-// One CTA.  Counts per expert, then every expert's run starts on a tile boundary (tiles of N rows); tile_expert names the
-// owner of each tile (-1 past the last one), row_pair the (token, slot) pair of each row (-1 for the padding of a run).
-// Within a run the pairs keep their order (by token, then slot): a warp walks the pair list for its experts with ballots.
+// One CTA of 32 warps.  Every expert's run of (token, slot) pairs starts on a tile boundary (tiles of N rows); tile_expert
+// names the owner of each tile (-1 past the last one), row_pair the pair of each row (-1 for the padding of a run).
+// Within a run the pairs keep their order (by token, then slot).  Warp w owns a contiguous stretch of the pair list and
+// walks it 32 pairs at a time; __match_any_sync gives every lane the lanes with the same expert, so a row of 32 pairs
+// costs one step whatever the number of experts.  First walk: counts per (warp, expert).  Then the runs' first rows
+// (a scan over experts) and every warp's first row inside each run (a scan over warps).  Second walk: places.
 constexpr int kGroupThreads = 1024;
-constexpr int kGroupChunk = 8192;
+constexpr int kGroupWarps = kGroupThreads / 32;
 
 __global__ void __launch_bounds__(kGroupThreads)
 moe_group_kernel(const int32_t* __restrict__ ids, int n_pairs, int experts, int N, int n_tiles, int32_t* __restrict__ tile_expert,
                  int32_t* __restrict__ row_pair) {
   extern __shared__ int32_t gsm[];
-  int32_t* cnt = gsm;                  // [experts]
-  int32_t* start = cnt + experts;      // [experts] next free row of the expert's run
-  int32_t* chunk = start + experts;    // [kGroupChunk] the pair list, a chunk at a time
+  int32_t* start = gsm;                 // [experts] first row of the expert's run
+  int32_t* wcnt = start + experts;      // [32 warps][experts] count, then next free row, of (warp, expert)
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int e = threadIdx.x; e < experts; e += kGroupThreads) cnt[e] = 0;
+  for (int i = threadIdx.x; i < kGroupWarps * experts; i += kGroupThreads) wcnt[i] = 0;
   for (int i = threadIdx.x; i < n_tiles * N; i += kGroupThreads) row_pair[i] = -1;
   for (int i = threadIdx.x; i < n_tiles; i += kGroupThreads) tile_expert[i] = -1;
-  // Two walks over the pair list, which goes through shared memory a chunk at a time (a global load inside the chain of
-  // ballots would pay its latency once per 32 pairs).  Warp w owns experts w, w + 32, ...: the first walk counts (no
-  // atomics: thousands of pairs on a few dozen counters serialise), the second one places.
+  const int rows = (n_pairs + 31) / 32, rpw = (rows + kGroupWarps - 1) / kGroupWarps;
+  const int r0 = warp * rpw, r1 = min(r0 + rpw, rows);
+  int32_t* mine = wcnt + warp * experts;
+  __syncthreads();
   for (int pass = 0; pass < 2; ++pass) {
-    for (int c0 = 0; c0 < n_pairs; c0 += kGroupChunk) {
-      const int cn = min(kGroupChunk, n_pairs - c0);
-      __syncthreads();
-      if (pass == 0 || n_pairs > kGroupChunk)
-        for (int i = threadIdx.x; i < cn; i += kGroupThreads) chunk[i] = ids[c0 + i];
-      __syncthreads();
-      for (int e = warp; e < experts; e += kGroupThreads / 32) {
-        if (pass == 1 && cnt[e] == 0) continue;
-        int pos = pass == 0 ? cnt[e] : start[e];
-        for (int b = 0; b < cn; b += 32) {
-          const int i = b + lane;
-          const bool mine = i < cn && chunk[i] == e;
-          const unsigned m = __ballot_sync(0xffffffffu, mine);
-          if (pass == 1 && mine) {
-            const int r = pos + __popc(m & ((1u << lane) - 1u));
-            if (r < n_tiles * N) row_pair[r] = c0 + i;
-          }
-          pos += __popc(m);
+    for (int r = r0; r < r1; ++r) {
+      const int i = r * 32 + lane;
+      int e = i < n_pairs ? ids[i] : -1;
+      if (e >= experts) e = -1;
+      const unsigned same = __match_any_sync(0xffffffffu, e);
+      if (e >= 0) {
+        const int before = __popc(same & ((1u << lane) - 1u));
+        if (pass == 1) {
+          const int row = mine[e] + before;
+          if (row < n_tiles * N) row_pair[row] = i;
         }
-        __syncwarp();
-        if (lane == 0) (pass == 0 ? cnt : start)[e] = pos;   // this warp alone owns expert e
+        __syncwarp(same);
+        if (before == 0) mine[e] += __popc(same);   // the group's first lane
       }
+      __syncwarp();
+    }
+    if (pass == 1) break;
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += kGroupThreads) {
+      int c = 0;
+      for (int w = 0; w < kGroupWarps; ++w) c += wcnt[w * experts + e];
+      start[e] = c;   // the expert's pairs; turned into its first row below
     }
     __syncthreads();
-    if (pass == 0 && threadIdx.x == 0) {
+    if (threadIdx.x == 0) {
       int run = 0;
       for (int e = 0; e < experts; ++e) {
-        const int nt = (cnt[e] + N - 1) / N;
+        const int nt = (start[e] + N - 1) / N;
         start[e] = run * N;
         for (int j = 0; j < nt && run + j < n_tiles; ++j) tile_expert[run + j] = e;
         run += nt;
       }
     }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += kGroupThreads) {
+      int at = start[e];
+      for (int w = 0; w < kGroupWarps; ++w) {
+        const int c = wcnt[w * experts + e];
+        wcnt[w * experts + e] = at;
+        at += c;
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -425,15 +438,20 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
   __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p);
   p += al256(rows * 2 * ff * 2);
   __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p);
-  B200_REQUIRE(experts <= 1024, B200_ERR_UNSUPPORTED, "experts: %d experts exceed the grouping kernel", experts);
-  B200_CUDA(launch(moe_group_kernel, dim3(1), dim3(kGroupThreads), (size_t)experts * 8 + (size_t)kGroupChunk * 4, s, ids, T * top, experts, N, n_tiles,
+  const size_t smem_grp = (size_t)experts * (1 + kGroupWarps) * 4;
+  B200_REQUIRE(smem_grp <= 200 * 1024, B200_ERR_UNSUPPORTED, "experts: %d experts exceed the grouping kernel", experts);
+  static bool done_grp[64] = {};
+  if (smem_grp > 48 * 1024) B200_CUDA(ensure_dynamic_smem(moe_group_kernel, 200 * 1024, done_grp));
+  B200_CUDA(launch(moe_group_kernel, dim3(1), dim3(kGroupThreads), smem_grp, s, ids, T * top, experts, N, n_tiles,
                    tile_expert, row_pair));
   B200_CUDA(launch(moe_gather_kernel, dim3((unsigned)rows), dim3(128), (size_t)0, s, x, (const int32_t*)tile_expert,
                    (const int32_t*)row_pair, N, top, width, xg));
   int rc;
   static const int fuse_env = getenv("B200_MOE_FUSE_SILU") ? atoi(getenv("B200_MOE_FUSE_SILU")) : 1;
-  if (fuse_env && ff % 64 == 0) {
-    // gate and up rows of a slab come in as two 64-row boxes; the epilogue activates (as the dense gate|up linear does)
+  if (fuse_env && ff % 64 == 0 && (N <= 64 || fuse_env > 1)) {
+    // gate and up rows of a slab come in as two 64-row boxes; the epilogue activates (as the dense gate|up linear does).
+    // Decode-sized tiles only: at 128 tokens per tile the epilogue's exponentials cost more than the pass they save
+    // (measured: 145 us against 119 + 19 us for 8192 rows of width 2048 into ff 1024)
     rc = linear_tc_grouped_gate_up(xg, width, N, n_tiles, w_gu, experts, ff, width, tile_expert, act, s);
     if (rc) return rc;
   } else {

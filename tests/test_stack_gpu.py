@@ -189,7 +189,8 @@ def test_router_against_the_oracle(experts, top, groups, keep):
     assert torch.allclose(got, torch.zeros(T, experts, dtype=torch.float64).scatter_(1, wi, ww), atol=1e-6)
 
 
-@pytest.mark.parametrize("T,W,experts,top,groups,keep", [(1, 72, 8, 3, 4, 2), (40, 136, 12, 4, 3, 3), (300, 64, 64, 6, 8, 3), (17, 520, 132, 5, 1, 1)])
+@pytest.mark.parametrize("T,W,experts,top,groups,keep", [(1, 72, 8, 3, 4, 2), (40, 136, 12, 4, 3, 3), (300, 64, 64, 6, 8, 3), (17, 520, 132, 5, 1, 1),
+                                                         (33, 80, 6, 2, 3, 2), (5, 64, 5, 5, 1, 1)])
 def test_router_with_tensor_core_logits(T, W, experts, top, groups, keep):
     """bf16 rows: logits from the tcgen05 linear with fp32 output (one and several token tiles, more experts than a slab),
     then the per-token selection.  The logits against float64, the choice against the oracle."""
@@ -311,6 +312,30 @@ def model_a():
 def model_odd():
     cfg = U.make_cfg(**ODD)
     return cfg, U.make_weights(cfg, seed=12)
+
+
+ODD2 = dict(width=54, vocab=61, scale=1.0, eps=1e-5, layers=[
+    U.layer(heads=3, kv_heads=1, dim=6, vdim=10, rot_dims=2, base=77.0, att_scale=0.4, moe=dict(experts=3, top=2, groups=1, keep=1, ff=7)),
+    U.layer(heads=1, kv_heads=1, dim=2, vdim=2, rot_dims=2, scaling=None, att_scale=1.0, moe=dict(experts=2, top=1, groups=2, keep=1, ff=1))])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_no_vector_access_fits(dtype):
+    """Width, ff and head sizes that are multiples of neither 8 nor 4 (the scalar forms of every kernel), one head, one
+    key/value pair per head, one expert per group, in both serving modes."""
+    cfg = U.make_cfg(**ODD2)
+    w = U.make_weights(cfg, seed=14)
+    ids = _prompt(cfg, 45, 9)
+    want = SO.forward(cfg, w, ids).numpy()
+    r = U.make_runner(cfg, w, dtype)
+    eng = U.make_engine(r)
+    got = U.replay(eng, [[("p", 20)], [("p", 2)]] + [[("p", 1)]] * 23, {"p": ids})["p"]
+    r.close()
+    e = U.rel_rms(got, want)
+    if dtype == "float32":
+        assert e.max() < F32_TOL
+    else:
+        assert np.median(e) < 0.03 and (e < 0.15).mean() > 0.9, (float(np.median(e)), float(e.max()))
 
 
 @pytest.mark.parametrize("which", ["a", "odd"])
