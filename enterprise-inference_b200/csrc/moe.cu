@@ -333,21 +333,30 @@ moe_group_kernel(const int32_t* __restrict__ ids, int n_pairs, int experts, int 
   int32_t* mine = wcnt + warp * experts;
   __syncthreads();
   for (int pass = 0; pass < 2; ++pass) {
-    for (int r = r0; r < r1; ++r) {
-      const int i = r * 32 + lane;
-      int e = i < n_pairs ? ids[i] : -1;
-      if (e >= experts) e = -1;
-      const unsigned same = __match_any_sync(0xffffffffu, e);
-      if (e >= 0) {
-        const int before = __popc(same & ((1u << lane) - 1u));
-        if (pass == 1) {
-          const int row = mine[e] + before;
-          if (row < n_tiles * N) row_pair[row] = i;
-        }
-        __syncwarp(same);
-        if (before == 0) mine[e] += __popc(same);   // the group's first lane
+    for (int rb = r0; rb < r1; rb += 8) {
+      int ev[8];   // eight rows' experts are requested before the first is used: the walk below is a dependent chain
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = (rb + u) * 32 + lane;
+        ev[u] = (rb + u < r1 && i < n_pairs) ? __ldg(ids + i) : -1;
       }
-      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (rb + u >= r1) break;   // warp-uniform
+        const int i = (rb + u) * 32 + lane;
+        const int e = ev[u] < experts ? ev[u] : -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0) {
+          const int before = __popc(same & ((1u << lane) - 1u));
+          if (pass == 1) {
+            const int row = mine[e] + before;
+            if (row < n_tiles * N) row_pair[row] = i;
+          }
+          __syncwarp(same);
+          if (before == 0) mine[e] += __popc(same);   // the group's first lane
+        }
+        __syncwarp();
+      }
     }
     if (pass == 1) break;
     __syncthreads();
