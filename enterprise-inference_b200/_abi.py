@@ -106,6 +106,9 @@ SIGNATURES = {
     "b200_layernorm_stream": (C.c_int, [_i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]),
     "b200_qk_norm_rotate_cache": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
                                             _i32, _i32, _f32, _i64, _vp]),
+    "b200_qk_norm_rotate_cache_wide": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
+                                                 _f32, _i64, _i32, _i32, _vp]),
+    "b200_rotate_back_rows": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _vp]),
     "b200_paged_attn_anydim_workspace_bytes": (_i64, [_i32]),
     "b200_paged_attn_anydim": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _i32,
                                          _i32, _f32, _i32, _vp, _vp]),

@@ -484,6 +484,24 @@ extern "C" int b200_qk_norm_rotate_cache(int32_t f32, const void* qkv, const flo
                               dim, vdim, block_size, eps, max_pos, (cudaStream_t)stream);
 }
 
+extern "C" int b200_qk_norm_rotate_cache_wide(const void* qkv, const float* qw, const float* kw, const int32_t* positions,
+                                              const int32_t* slots, const float* rot, int32_t rot_dims, const float* vrot, void* q_out,
+                                              void* kc, void* vc, int32_t T, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                                              int32_t block_size, float eps, int64_t max_pos, int32_t k_row, int32_t v_row, void* stream) {
+  B200_REQUIRE(qkv && qw && kw && positions && slots && q_out && kc && vc && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 &&
+                   block_size > 0 && max_pos > 0 && k_row >= dim && v_row >= vdim && k_row % 2 == 0 && v_row % 2 == 0,
+               B200_ERR_INVALID, "qk_norm_rotate_cache_wide: bad argument");
+  return qk_norm_rotate_cache(false, qkv, qw, kw, positions, slots, rot, rot ? rot_dims : 0, vrot, nullptr, kc, vc, T, heads, kv_heads,
+                              dim, vdim, block_size, eps, max_pos, (cudaStream_t)stream, (__nv_bfloat16*)q_out, k_row, v_row);
+}
+
+extern "C" int b200_rotate_back_rows(const void* in, int32_t in_row, void* out, const int32_t* positions, const float* vrot, int32_t T,
+                                     int32_t heads, int32_t vdim, int64_t max_pos, void* stream) {
+  B200_REQUIRE(in && out && positions && T >= 0 && heads > 0 && vdim > 0 && max_pos > 0, B200_ERR_INVALID, "rotate_back_rows: bad argument");
+  return rotate_back_rows((const __nv_bfloat16*)in, in_row, (__nv_bfloat16*)out, positions, vrot, T, heads, vdim, max_pos,
+                          (cudaStream_t)stream);
+}
+
 extern "C" int64_t b200_paged_attn_anydim_workspace_bytes(int32_t T) { return paged_attn_anydim_workspace_bytes(T); }
 
 extern "C" int b200_paged_attn_anydim(int32_t f32, const float* q, const void* kc, const void* vc, const int32_t* block_table,

@@ -441,6 +441,17 @@ B200_API int b200_qk_norm_rotate_cache(int32_t f32, const void* qkv, const float
                               const float* vrot, float* q_out, void* k_cache, void* v_cache, int32_t n_tokens, int32_t heads,
                               int32_t kv_heads, int32_t dim, int32_t vdim, int32_t block_size, float eps, int64_t max_pos,
                               void* stream);
+/* The same over bf16 rows for attention kernels built for wider heads: bf16 queries [T][heads][k_row], cache rows of k_row /
+ * v_row elements; the tail beyond dim / vdim is written as zero. */
+B200_API int b200_qk_norm_rotate_cache_wide(const void* qkv, const float* q_norm_w, const float* k_norm_w, const int32_t* positions,
+                                            const int32_t* slots, const float* rot, int32_t rot_dims, const float* vrot, void* q_out,
+                                            void* k_cache, void* v_cache, int32_t n_tokens, int32_t heads, int32_t kv_heads, int32_t dim,
+                                            int32_t vdim, int32_t block_size, float eps, int64_t max_pos, int32_t k_row, int32_t v_row,
+                                            void* stream);
+/* bf16 attention output rows [T][heads][in_row] -> [T][heads][vdim], each pair (2m, 2m+1) turned back by the row's position
+ * (vrot: the value table, or null for packing alone).  in == out only when in_row == vdim. */
+B200_API int b200_rotate_back_rows(const void* in, int32_t in_row, void* out, const int32_t* positions, const float* vrot,
+                                   int32_t n_tokens, int32_t heads, int32_t vdim, int64_t max_pos, void* stream);
 /* Causal paged attention of fp32 queries [T][heads*dim] over caches [block][kv_heads][block_size][dim | vdim]; out
  * [T][heads*vdim].  vrot != NULL: the output of row t is rotated by -positions[t].  shared_tiles 0: one CTA per (row, head);
  * 1: runs of consecutive rows of a sequence share K/V tiles (workspace: b200_paged_attn_anydim_workspace_bytes(T)). */

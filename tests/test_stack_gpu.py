@@ -117,6 +117,67 @@ def test_qk_norm_rotation_and_cache_write(heads, kv, dim, vdim, rot_dims, scalin
     assert int((kcc.abs().sum(-1) > 0).sum()) == T * kv      # nothing else was written
 
 
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot_dims", [(4, 2, 64, 96, 32), (2, 1, 128, 128, 128), (3, 3, 80, 64, 0)])
+def test_wide_cache_rows_keep_a_zero_tail(heads, kv, dim, vdim, rot_dims):
+    """bf16 rows into 128-wide query and cache rows: the head's dimensions match the oracle, the tail is written as zero (the
+    caches start as NaN), other slots stay untouched."""
+    g = torch.Generator().manual_seed(heads + dim)
+    T, bs, nb, eps, base, R = 5, 4, 6, 1e-5, 1000.0, 128
+    pos = torch.tensor([0, 1, 9, 300, 511], dtype=torch.int32)
+    slots = torch.tensor([0, 1, 2 * bs + 3, 5 * bs, 4 * bs + 1], dtype=torch.int32)
+    qn, kn, vn = heads * dim, kv * dim, kv * vdim
+    qkv = U.bf16_exact(torch.randn(T, qn + kn + vn, generator=g) * 2)
+    qw, kw = 1 + 0.3 * torch.randn(qn, generator=g), 1 + 0.3 * torch.randn(kn, generator=g)
+    rot, vrot = _tables(base, rot_dims, None, vdim, 512)
+    kc = torch.full((nb, kv, bs, R), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((nb, kv, bs, R), float("nan"), dtype=torch.bfloat16, device=DEV)
+    qo = torch.full((T, heads, R), float("nan"), dtype=torch.bfloat16, device=DEV)
+    check(lib().b200_qk_norm_rotate_cache_wide(dev(qkv, torch.bfloat16).data_ptr(), dev(qw).data_ptr(), dev(kw).data_ptr(),
+                                               dev(pos).data_ptr(), dev(slots).data_ptr(), dev(rot).data_ptr() if rot is not None else None,
+                                               rot_dims, dev(vrot).data_ptr(), qo.data_ptr(), kc.data_ptr(), vc.data_ptr(), T, heads, kv,
+                                               dim, vdim, bs, eps, 512, R, R, None))
+    sync()
+    x = qkv.double()
+    q = (SO.unit_rms(x[:, :qn], eps) * qw.double()).view(T, heads, dim)
+    k = (SO.unit_rms(x[:, qn:qn + kn], eps) * kw.double()).view(T, kv, dim)
+    v = SO.unit_rms(x[:, qn + kn:].view(T, kv, vdim), eps)
+    p = pos.double()
+    if rot_dims:
+        f, mag = SO.rotary_frequencies(base, rot_dims, None)
+        q, k = SO.rotate_pairs(q, p[:, None, None] * f, mag), SO.rotate_pairs(k, p[:, None, None] * f, mag)
+    v = SO.rotate_pairs(v, p[:, None, None] * SO.rotary_frequencies(base, vdim)[0])
+    qc, kcc, vcc = qo.cpu().double(), kc.cpu().double(), vc.cpu().double()
+    assert torch.allclose(qc[..., :dim], q, atol=3e-2, rtol=1e-2) and (qc[..., dim:] == 0).all()
+    written = set()
+    for t in range(T):
+        b, o = int(slots[t]) // bs, int(slots[t]) % bs
+        written.add((b, o))
+        assert torch.allclose(kcc[b, :, o, :dim], k[t], atol=3e-2, rtol=1e-2) and (kcc[b, :, o, dim:] == 0).all(), t
+        assert torch.allclose(vcc[b, :, o, :vdim], v[t], atol=3e-2, rtol=1e-2) and (vcc[b, :, o, vdim:] == 0).all(), t
+    for b in range(nb):
+        for o in range(bs):
+            if (b, o) not in written:
+                assert torch.isnan(kcc[b, :, o]).all() and torch.isnan(vcc[b, :, o]).all()
+
+
+@pytest.mark.parametrize("heads,vdim,row,rotated", [(3, 96, 128, True), (2, 128, 128, True), (4, 64, 128, False), (1, 2, 2, True)])
+def test_output_rows_turn_back_and_pack(heads, vdim, row, rotated):
+    g = torch.Generator().manual_seed(vdim)
+    T, base = 6, 1000.0
+    pos = torch.tensor([0, 1, 5, 130, 400, 511], dtype=torch.int32)
+    a = U.bf16_exact(torch.randn(T, heads, row, generator=g))
+    vrot = pkg("config").RotarySpec(base=base, dims=vdim).table(512)
+    src = dev(a, torch.bfloat16)
+    out = src if row == vdim else torch.full((T, heads, vdim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    check(lib().b200_rotate_back_rows(src.data_ptr(), row, out.data_ptr(), dev(pos).data_ptr(), dev(vrot).data_ptr() if rotated else None,
+                                      T, heads, vdim, 512, None))
+    sync()
+    want = a[..., :vdim].double()
+    if rotated:
+        want = SO.rotate_pairs(want, -pos.double()[:, None, None] * SO.rotary_frequencies(base, vdim)[0])
+    assert torch.allclose(out.cpu().double(), want, atol=2e-2, rtol=1e-2)
+
+
 def _attn_oracle(q, k, v, ctx, scale, fv, qpos):
     """q [H, d], k [n, G, d], v [n, G, e] of one sequence; the row sees the first ctx keys."""
     H, G = q.shape[0], k.shape[1]
@@ -252,7 +313,7 @@ def _experts_rounded(x, ids, wts, gate, up, down):
 
 
 @pytest.mark.parametrize("T,W,ff,experts,top", [(1, 64, 64, 8, 2), (3, 136, 72, 5, 5), (40, 64, 200, 4, 2), (300, 256, 136, 6, 3),
-                                                (700, 128, 64, 3, 1), (3000, 64, 64, 4, 3)])
+                                                (700, 128, 64, 3, 1), (3000, 64, 64, 4, 3), (100, 64, 128, 4, 1), (200, 72, 64, 4, 1)])
 def test_experts_tensor_core_form(T, W, ff, experts, top):
     """Every token-tile size, runs that end inside a tile, experts nobody chose, slab rows past an expert's last row, ff
     that is and is not a multiple of 64 (activation in the epilogue or as a step of its own), more pairs than the grouping
