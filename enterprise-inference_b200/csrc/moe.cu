@@ -1,12 +1,13 @@
 // Mixture-of-experts feed-forward: a softmax router with a selection bias and group-limited top-k choice, and the chosen
 // experts' gated feed-forward (down(silu(gate x) * (up x))).
 //
-// Router (one CTA per token, fp32 throughout): z = W_r x, s = softmax(z) over all experts; the CHOICE uses s + bias, the
+// Router (fp32 throughout; fp32 rows: one CTA per token computes logits and choice; bf16 rows: the logits are a tcgen05
+// linear with unrounded fp32 output, then one warp per token chooses): z = W_r x, s = softmax(z) over all experts; the CHOICE uses s + bias, the
 // mixing weights use s itself, not renormalised.  With groups: the experts form `groups` equal runs of neighbours, a
 // group's score is its largest choice score, only the `keep` best groups stay eligible (the others count as -inf), then
 // the `top` largest eligible choice scores win.  Ties go to the lowest index.
 //
-// Experts: two forms over the same weights ([expert][2 ff][width]: gate rows then up rows; [expert][width][ff]):
+// Experts: three forms over the same weights ([expert][2 ff][width]: gate rows then up rows; [expert][width][ff]):
 //  * token form (decode-sized steps): one CTA per (token, chosen slot) streams that expert's three matrices once;
 //  * grouped form (prefill-sized steps): tokens are bucketed by expert on the device (deterministic order: by token, then
 //    slot), and one CTA per (expert, tile of 16 of its tokens) streams the expert's weights once for the whole tile.
