@@ -26,19 +26,30 @@ class ModelCfg(C.Structure):
 class StackLayer(C.Structure):
     """struct b200_stack_layer"""
     _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "rot_dims", "rot_table", "vrot_table")] + \
-               [("scale", C.c_float)] + [(n, C.c_int32) for n in ("mlp", "experts", "top", "groups", "keep", "ff")]
+               [("scale", C.c_float)] + [(n, C.c_int32) for n in ("mlp", "experts", "top", "groups", "keep", "ff")] + \
+               [(n, C.c_int32) for n in ("kv_rank", "rot_dim", "mixer_flags")] + [("gate_cap", C.c_float)] + \
+               [(n, C.c_int32) for n in ("act", "ungated", "sigmoid_scores", "weight_input", "shared_ff")]
 
 
 class StackCfg(C.Structure):
     """struct b200_stack_cfg"""
     _fields_ = [(n, C.c_int32) for n in ("width", "vocab", "n_layers")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)] + \
-               [(n, C.c_int32) for n in ("f32", "block_size", "max_tokens", "max_blocks_per_seq", "max_logit_rows")]
+               [(n, C.c_int32) for n in ("f32", "block_size", "max_tokens", "max_blocks_per_seq", "max_logit_rows")] + \
+               [(n, C.c_int32) for n in ("form", "canon_taps", "depth_avg", "bigram_buckets", "bigram_mul_prev", "bigram_mul_cur")] + \
+               [("logit_softcap", C.c_float), ("n_state_slots", C.c_int32)]
 
 
-MIXER_ATTENTION, MLP_NONE, MLP_MOE = 1, 0, 1
+MIXER_ATTENTION, MIXER_LATENT, MIXER_MLSTM = 1, 2, 3
+MLP_NONE, MLP_MOE, MLP_DENSE = 0, 1, 2
+ACT_SILU, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2
+ACTS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2}
+FORM_SANDWICH, FORM_PARALLEL = 0, 1
+MIXF_SINK, MIXF_GATE = 1, 2
 (SW_EMBED, SW_FINAL_NORM, SW_HEAD, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_QKV, SW_Q_NORM,
- SW_K_NORM, SW_O, SW_ROUTER, SW_ROUTER_BIAS, SW_EXPERT_GATE_UP, SW_EXPERT_DOWN) = range(15)
-SW_F32 = {SW_FINAL_NORM, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_Q_NORM, SW_K_NORM, SW_ROUTER_BIAS}
+ SW_K_NORM, SW_O, SW_ROUTER, SW_ROUTER_BIAS, SW_EXPERT_GATE_UP, SW_EXPERT_DOWN, SW_BIGRAM, SW_CANON, SW_DEPTH_AVG, SW_UK_T, SW_UV,
+ SW_SINK, SW_GATES, SW_GATES_BIAS, SW_HEAD_NORM, SW_MLP_GATE_UP, SW_MLP_DOWN, SW_SHARED_UP, SW_SHARED_DOWN) = range(28)
+SW_F32 = {SW_FINAL_NORM, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_Q_NORM, SW_K_NORM, SW_ROUTER_BIAS,
+          SW_CANON, SW_DEPTH_AVG, SW_SINK, SW_GATES_BIAS, SW_HEAD_NORM}
 
 W_EMBED, W_LN1, W_QKV, W_QKV_BIAS, W_O, W_LN2, W_GATE_UP, W_DOWN, W_FINAL_NORM, W_LM_HEAD, W_GATE_UP_INTERLEAVED = range(11)
 
@@ -102,6 +113,9 @@ SIGNATURES = {
     "b200_stack_cache_dims": (C.c_int, [_vp, _i32, _vp, _vp]),
     "b200_stack_set_rot_table": (C.c_int, [_vp, _i32, _vp, _i64, _i32]),
     "b200_stack_set_stream_tap": (C.c_int, [_vp, _vp]),
+    "b200_stack_state_bytes": (_i64, [_vp]),
+    "b200_stack_set_state": (C.c_int, [_vp, _vp]),
+    "b200_stack_set_step_slots": (C.c_int, [_vp, _vp, _i32]),
     "b200_ctx_logits_last_f32": (C.c_int, [_vp, _i32, _vp, _vp]),
     "b200_layernorm_stream": (C.c_int, [_i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]),
     "b200_qk_norm_rotate_cache": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,

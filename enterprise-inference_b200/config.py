@@ -286,8 +286,153 @@ class BopilornConfig:
                               norm_eps=float((c.get("norm") or {}).get("eps", 1e-5)), layers=layers)
 
 
+# ---- Dupolorn ---------------------------------------------------------------------------------------------------------------
+@dataclass
+class LatentAttentionSpec:
+    """Attention over one cached latent vector per token: per head `dim` plain and `rot_dim` rotated query/key dimensions, the
+    rotated key part shared by all heads, keys and values expanded from the latent of `kv_rank` dimensions.  sink: a learned
+    per-head term in the softmax denominator; gate: sigmoid output gate read from the mixer's input."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot: Optional[RotarySpec] = None
+    sink: bool = False
+    gate: bool = False
+    kind: str = "latent"
+
+
+@dataclass
+class MLSTMSpec:
+    """Matrix-memory recurrence: `heads` heads of key size `dim` and value size `vdim`; the log gates are capped by
+    cap * tanh(z / cap)."""
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+    kind: str = "mlstm"
+
+
+@dataclass
+class FeedForwardSpec:
+    """kind "dense": down(act(gate h) * (up h)).  kind "moe": `experts` ungated experts down(act(up h)) of which a token uses
+    `top`, chosen by sigmoid scores that scale the expert's input; `shared_ff` > 0 adds one expert every token uses."""
+    kind: str
+    ff: int
+    act: str = "gelu_tanh"
+    experts: int = 0
+    top: int = 0
+    shared_ff: int = 0
+
+
+@dataclass
+class ParallelLayerSpec:
+    mixer: object                     # LatentAttentionSpec | MLSTMSpec
+    mlp: Optional[FeedForwardSpec] = None
+
+
+@dataclass
+class DupolornConfig:
+    """Dupolorn: decoder-only, layers in the parallel form x += mixer(conv(norm1 x)) + ff(norm2 x) with one-number RMS norms, a
+    causal per-channel input convolution, a depth-weighted average over all layer results, a hashed bigram embedding and
+    capped logits.  Mixers: latent attention (plain, or with sink and output gate) and mLSTM."""
+    name: str = "dupolorn"
+    width: int = 256
+    vocab: int = 1024
+    embed_scale: float = 1.0
+    norm_eps: float = 1e-6
+    canon_taps: int = 0
+    bigram_buckets: int = 0
+    bigram_mul_prev: int = 0
+    bigram_mul_cur: int = 0
+    logit_softcap: float = 0.0
+    depth_avg: bool = True
+    layers: List[ParallelLayerSpec] = field(default_factory=list)
+    architecture: str = "Dupolorn"
+
+    @property
+    def hidden(self) -> int:
+        return self.width
+
+    @property
+    def n_layers(self) -> int:
+        return len(self.layers)
+
+    @property
+    def needs_state(self) -> bool:
+        return self.canon_taps > 1 or self.bigram_buckets > 0 or any(isinstance(L.mixer, MLSTMSpec) for L in self.layers)
+
+    def to_dict(self):
+        return asdict(self)
+
+    def _layer_params(self, L: ParallelLayerSpec, active_only: bool) -> int:
+        W, a, n = self.width, L.mixer, 0
+        if isinstance(a, MLSTMSpec):
+            n += W * (2 * a.heads * a.dim + 2 * a.heads * a.vdim + 2 * a.heads) + a.heads * a.vdim * W
+        else:
+            n += W * (a.heads * (a.dim + a.rot_dim) + a.kv_rank + a.rot_dim + (a.heads * a.vdim if a.gate else 0))
+            n += a.heads * a.kv_rank * (a.dim + a.vdim) + a.heads * a.vdim * W
+        f = L.mlp
+        if f and f.kind == "dense":
+            n += 3 * f.ff * W
+        elif f:
+            n += f.experts * W + (f.top if active_only else f.experts) * 2 * f.ff * W + 2 * f.shared_ff * W
+        return n
+
+    def decode_params(self) -> int:
+        """Weights one decode row touches (chosen experts only)."""
+        return self.vocab * self.width + sum(self._layer_params(L, True) for L in self.layers)
+
+    def weight_bytes(self) -> int:
+        return 2 * (2 * self.vocab * self.width + (self.bigram_buckets + 1) * self.width * (1 if self.bigram_buckets else 0)
+                    + sum(self._layer_params(L, False) for L in self.layers))
+
+    def kv_bytes_per_token(self, f32: bool = False) -> int:
+        return sum(L.mixer.kv_rank + L.mixer.rot_dim for L in self.layers if isinstance(L.mixer, LatentAttentionSpec)) * (4 if f32 else 2)
+
+    @staticmethod
+    def from_dict(c: dict, name: str = "dupolorn") -> "DupolornConfig":
+        layers = []
+        for i, l in enumerate(c["layers"]):
+            kind, m = l.get("type"), l["mixer"]
+            if kind in ("latent_attention", "latent_attention_2"):
+                rot = None
+                r = m.get("rot")
+                if r and int(r["dims"]) > 0 and int(m.get("rot_dim", 0)) > 0:
+                    rot = RotarySpec(base=float(r["base"]), dims=int(r["dims"]))
+                    if rot.dims > int(m["rot_dim"]) or rot.dims % 2:
+                        raise ValueError(f"layer {i}: {rot.dims} rotated dimensions in a part of {m['rot_dim']}")
+                second = kind == "latent_attention_2"
+                mixer = LatentAttentionSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m.get("rot_dim", 0)), vdim=int(m["vdim"]),
+                                            kv_rank=int(m["kv_rank"]), scale=float(m["scale"]), rot=rot, sink=second, gate=second)
+            elif kind == "mlstm":
+                mixer = MLSTMSpec(heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), gate_cap=float(m["gate_cap"]))
+            else:
+                raise ValueError(f"layer {i}: unsupported mixer type {kind!r} (this design has latent_attention, latent_attention_2, mlstm)")
+            mlp = None
+            f = l.get("mlp")
+            if f:
+                if f.get("kind") == "dense":
+                    mlp = FeedForwardSpec(kind="dense", ff=int(f["ff"]), act="gelu_tanh")
+                elif f.get("kind") == "moe":
+                    sh = f.get("shared") or {}
+                    mlp = FeedForwardSpec(kind="moe", ff=int(f["expert"]["ff"]), act="relu2", experts=int(f["router"]["experts"]),
+                                          top=int(f["router"]["top"]), shared_ff=int(sh.get("ff", 0)))
+                else:
+                    raise ValueError(f"layer {i}: unsupported feed-forward kind {f.get('kind')!r}")
+            layers.append(ParallelLayerSpec(mixer=mixer, mlp=mlp))
+        emb = c.get("embedding") or {}
+        bg = emb.get("bigram") or {}
+        return DupolornConfig(name=name, width=int(c["width"]), vocab=int(c["vocab"]), embed_scale=float(emb.get("scale", 1.0)),
+                              norm_eps=float((c.get("norm") or {}).get("eps", 1e-6)), canon_taps=int((c.get("canon") or {}).get("taps", 0)),
+                              bigram_buckets=int(bg.get("buckets", 0)), bigram_mul_prev=int(bg.get("mul_prev", 0)),
+                              bigram_mul_cur=int(bg.get("mul_cur", 0)), logit_softcap=float(c.get("logit_softcap") or 0.0), layers=layers)
+
+
 # config.json "architecture" -> reader.  HF-style configs (model_type) go through from_hf_config.
-ARCHITECTURES = {"Bopilorn": BopilornConfig.from_dict}
+ARCHITECTURES = {"Bopilorn": BopilornConfig.from_dict, "Dupolorn": DupolornConfig.from_dict}
 
 
 def load_model_config(path: str):

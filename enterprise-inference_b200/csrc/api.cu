@@ -874,7 +874,8 @@ static int run_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
                       (uint64_t)a.block_table, (uint64_t)a.row_to_seq, (uint64_t)a.ctx_lens,
                       (uint64_t)a.logit_rows,  (uint64_t)a.out_tokens, (uint64_t)a.out_logits,
                       (uint64_t)a.bt_stride,   (uint64_t)a.T,          (uint64_t)pow2_bucket(a.max_ctx),
-                      (uint64_t)a.R,           (uint64_t)launch_opts().pdl, (uint64_t)a.n_seqs, (uint64_t)a.prev_tokens}};
+                      (uint64_t)a.R,           (uint64_t)launch_opts().pdl, (uint64_t)a.n_seqs,
+                      (uint64_t)a.prev_tokens ^ ((uint64_t)a.seq_slots << 17 | (uint64_t)a.seq_slots >> 47)}};
   auto it = c->graph_cache.find(key);
   if (it == c->graph_cache.end()) {
     StepArgs b = a;
@@ -1027,6 +1028,7 @@ extern "C" int b200_decode_step(b200_ctx* c, const int32_t* ids, const int32_t* 
                "decode_step: null argument");
   StepArgs a{ids, positions, slot_mapping, block_table, row_to_seq, ctx_lens, logit_rows, bt_stride, n_tokens,
              max_ctx_len, logit_rows ? n_logit_rows : n_tokens, out_token_ids, out_logits};
+  if (c->stack && stack_state_slots(c) > 0) stack_step_slots(c, &a.seq_slots, &a.n_seqs);
   return run_step(c, a, (cudaStream_t)stream);
 }
 
@@ -1043,12 +1045,14 @@ extern "C" int b200_decode_step_host(b200_ctx* c, const int32_t* host_packed, in
   // (T, rows, seqs, bt_stride) only, so steps of the same shape replay the same captured graph.
   const int64_t T = n_tokens;
   int32_t* d = c->d_meta;
-  const int64_t n_ints = 5 * T + n_logit_rows + (int64_t)n_seqs * bt_stride;
+  const bool slots = c->stack && stack_state_slots(c) > 0;
+  const int64_t n_ints = 5 * T + n_logit_rows + (int64_t)n_seqs * bt_stride + (slots ? n_seqs : 0);
   B200_REQUIRE(n_ints <= c->meta_ints, B200_ERR_INVALID, "decode_step_host: metadata larger than the ctx buffer");
   B200_CUDA(cudaMemcpyAsync(d, host_packed, (size_t)n_ints * 4, cudaMemcpyHostToDevice, s));
   StepArgs a{d, d + T, d + 2 * T, d + 5 * T + n_logit_rows, d + 4 * T, d + 3 * T, d + 5 * T, bt_stride, n_tokens,
              max_ctx_len, n_logit_rows, c->d_tokens, nullptr};
   a.n_seqs = n_seqs;
+  if (slots) a.seq_slots = d + 5 * T + n_logit_rows + (int64_t)n_seqs * bt_stride;
   a.prev_tokens = c->d_tokens;
   a.n_prev = c->max_logit_rows;
   int rc = run_step(c, a, s);

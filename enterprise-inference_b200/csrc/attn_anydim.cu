@@ -51,7 +51,7 @@ paged_attn_rows_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
                        const int32_t* __restrict__ block_table, int bt_stride, const int32_t* __restrict__ row_to_seq,
                        const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ positions,
                        const float* __restrict__ vrot, int64_t max_pos, AT* __restrict__ out, int heads, int kv_heads,
-                       int dim, int vdim, int block_size, float scale) {
+                       int dim, int vdim, int block_size, float scale, int kst, int vst, const float* __restrict__ sink) {
   extern __shared__ float sm[];
   float* qs = sm;                 // [dim]
   float* ps = qs + dim;           // [128] weights of the tile
@@ -76,7 +76,7 @@ paged_attn_rows_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
     int blk = 0;
     if (j < ctx) {
       blk = bt[j / block_size];
-      const CT* kp = kc + (((int64_t)blk * kv_heads + g) * block_size + j % block_size) * dim;
+      const CT* kp = kc + (((int64_t)blk * kv_heads + g) * block_size + j % block_size) * kst;
       float a = 0.f;
       for (int d = 0; d < dim; ++d) a = fmaf(qs[d], cache_load<CT>(kp, d), a);
       sc = a * scale;
@@ -98,13 +98,19 @@ paged_attn_rows_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
       if (d < vdim) {
         float a = acc[i] * corr;
         for (int jj = 0; jj < n; ++jj) {
-          const CT* vp = vc + (((int64_t)blk_of[jj] * kv_heads + g) * block_size + (base + jj) % block_size) * vdim;
+          const CT* vp = vc + (((int64_t)blk_of[jj] * kv_heads + g) * block_size + (base + jj) % block_size) * vst;
           a = fmaf(ps[jj], cache_load<CT>(vp, d), a);
         }
         acc[i] = a;
       }
     }
     __syncthreads();
+  }
+  if (sink != nullptr) {   // one more term of the denominator, without key or value
+    const float sk = sink[h], mn = fmaxf(m, sk), corr = expf(m - mn);
+    l = l * corr + expf(sk - mn);
+#pragma unroll
+    for (int i = 0; i < kAdMaxVPer; ++i) acc[i] *= corr;
   }
   const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
@@ -162,7 +168,7 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
                        const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ positions,
                        const float* __restrict__ vrot, int64_t max_pos, AT* __restrict__ out,
                        const int32_t* __restrict__ runs, const int32_t* __restrict__ n_runs, int heads, int kv_heads, int dim,
-                       int vdim, int block_size, float scale) {
+                       int vdim, int block_size, float scale, int kcs, int vcs, const float* __restrict__ sink) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_launch_dependents();
@@ -198,11 +204,11 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
     const int n = min(kTileKeys, ctx_max - base);
     for (int i = threadIdx.x; i < n * dim; i += kTcThreads) {
       const int jj = i / dim, d = i % dim, j = base + jj;
-      Ks[jj * kst + d] = cache_load<CT>(kc, (((int64_t)bt[j / block_size] * kv_heads + g) * block_size + j % block_size) * dim + d);
+      Ks[jj * kst + d] = cache_load<CT>(kc, (((int64_t)bt[j / block_size] * kv_heads + g) * block_size + j % block_size) * kcs + d);
     }
     for (int i = threadIdx.x; i < n * vdim; i += kTcThreads) {
       const int jj = i / vdim, d = i % vdim, j = base + jj;
-      Vs[jj * vst + d] = cache_load<CT>(vc, (((int64_t)bt[j / block_size] * kv_heads + g) * block_size + j % block_size) * vdim + d);
+      Vs[jj * vst + d] = cache_load<CT>(vc, (((int64_t)bt[j / block_size] * kv_heads + g) * block_size + j % block_size) * vcs + d);
     }
     __syncthreads();
 #pragma unroll
@@ -249,7 +255,13 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
     const int qi = warp + k * nw;
     if (qi < nq) {
       const int r = qi / G, hh = qi % G, t = t0 + r;
-      const float inv = l[k] > 0.f ? 1.0f / l[k] : 0.f;
+      float lk = l[k], osc = 1.f;
+      if (sink != nullptr) {
+        const float sk = sink[g * G + hh], mn = fmaxf(m[k], sk);
+        osc = expf(m[k] - mn);
+        lk = lk * osc + expf(sk - mn);
+      }
+      const float inv = lk > 0.f ? osc / lk : 0.f;
       int pos = positions[t];
       pos = pos < 0 ? 0 : (pos >= max_pos ? (int)max_pos - 1 : pos);
       const float* cs = vrot ? vrot + (int64_t)pos * 2 * vhalf : nullptr;
@@ -275,7 +287,7 @@ template <typename CT, typename AT>
 static int paged_attn_anydim_t(const float* q, const void* kc, const void* vc, const int32_t* block_table, int bt_stride,
                                const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, const float* vrot,
                                int64_t max_pos, void* out, int T, int heads, int kv_heads, int dim, int vdim, int block_size,
-                               float scale, int plan, void* ws, cudaStream_t s) {
+                               float scale, int plan, void* ws, cudaStream_t s, int kst, int vst, const float* sink) {
   const int G = heads / kv_heads;
   const size_t smem_runs = ((size_t)kTileKeys * (dim + 1 + vdim) + (size_t)kRunRows * G * (dim + vdim)) * 4;
   if (plan != 0 && ws != nullptr && kRunRows * G <= 16 * (kTcThreads / 32) && smem_runs <= 200 * 1024) {
@@ -286,13 +298,13 @@ static int paged_attn_anydim_t(const float* q, const void* kc, const void* vc, c
     if (smem_runs > 48 * 1024) B200_CUDA(ensure_dynamic_smem(paged_attn_runs_kernel<CT, AT>, 200 * 1024, done));
     B200_CUDA(launch(paged_attn_runs_kernel<CT, AT>, dim3(T, kv_heads), dim3(kTcThreads), smem_runs, s, q, (const CT*)kc,
                      (const CT*)vc, block_table, bt_stride, row_to_seq, ctx_lens, positions, vrot, max_pos, (AT*)out,
-                     (const int32_t*)runs, (const int32_t*)n_runs, heads, kv_heads, dim, vdim, block_size, scale));
+                     (const int32_t*)runs, (const int32_t*)n_runs, heads, kv_heads, dim, vdim, block_size, scale, kst, vst, sink));
     return B200_OK;
   }
   const size_t smem = ((size_t)dim + kAdThreads + vdim) * 4;
   B200_CUDA(launch(paged_attn_rows_kernel<CT, AT>, dim3(T, heads), dim3(kAdThreads), smem, s, q, (const CT*)kc, (const CT*)vc,
                    block_table, bt_stride, row_to_seq, ctx_lens, positions, vrot, max_pos, (AT*)out, heads, kv_heads, dim, vdim,
-                   block_size, scale));
+                   block_size, scale, kst, vst, sink));
   return B200_OK;
 }
 
@@ -301,15 +313,17 @@ static int paged_attn_anydim_t(const float* q, const void* kc, const void* vc, c
 int paged_attn_anydim(bool f32, const float* q, const void* kc, const void* vc, const int32_t* block_table, int bt_stride,
                       const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, const float* vrot,
                       int64_t max_pos, void* out, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float scale,
-                      int plan, void* ws, cudaStream_t s) {
+                      int plan, void* ws, cudaStream_t s, int kstride, int vstride, const float* sink) {
   if (T == 0) return B200_OK;
+  const int kst = kstride > 0 ? kstride : dim, vst = vstride > 0 ? vstride : vdim;
+  B200_REQUIRE(kst >= dim && vst >= vdim, B200_ERR_INVALID, "attention: cache rows of %d / %d elements for heads of %d / %d", kst, vst, dim, vdim);
   B200_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, B200_ERR_INVALID, "attention: %d heads over %d kv heads", heads, kv_heads);
   B200_REQUIRE(vdim <= kAdThreads * kAdMaxVPer && dim <= 8192, B200_ERR_UNSUPPORTED, "attention: head sizes %d / %d too large", dim, vdim);
   return f32 ? paged_attn_anydim_t<float, float>(q, kc, vc, block_table, bt_stride, row_to_seq, ctx_lens, positions, vrot, max_pos,
-                                                 out, T, heads, kv_heads, dim, vdim, block_size, scale, plan, ws, s)
+                                                 out, T, heads, kv_heads, dim, vdim, block_size, scale, plan, ws, s, kst, vst, sink)
              : paged_attn_anydim_t<__nv_bfloat16, __nv_bfloat16>(q, kc, vc, block_table, bt_stride, row_to_seq, ctx_lens,
                                                                  positions, vrot, max_pos, out, T, heads, kv_heads, dim, vdim,
-                                                                 block_size, scale, plan, ws, s);
+                                                                 block_size, scale, plan, ws, s, kst, vst, sink);
 }
 
 }  // namespace b200

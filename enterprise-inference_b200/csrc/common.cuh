@@ -79,6 +79,16 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// activations of the feed-forwards (b200_act_kind), fp32
+__device__ __forceinline__ float act_apply(float z, int kind) {
+  if (kind == B200_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (kind == B200_ACT_RELU2) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  return z / (1.0f + expf(-z));
+}
+
 // ---- Programmatic dependent launch -------------------------------------------------------
 // Every kernel of the step waits for its predecessor's memory here and lets its successor
 // start its prologue early; with no PDL attribute on the launch both are no-ops.
@@ -286,16 +296,58 @@ int64_t paged_attn_anydim_workspace_bytes(int T);
 int paged_attn_anydim(bool f32, const float* q, const void* kc, const void* vc, const int32_t* block_table, int bt_stride,
                       const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, const float* vrot,
                       int64_t max_pos, void* out, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float scale,
-                      int plan, void* ws, cudaStream_t s);
+                      int plan, void* ws, cudaStream_t s, int kstride = 0, int vstride = 0, const float* sink = nullptr);
+// kstride / vstride: elements per cache row when they exceed dim / vdim (0: dim / vdim; the value cache may then be the key
+// cache itself, a value being the leading vdim entries of the row); sink [heads]: exp(sink[h]) joins the softmax denominator
 // mixture of experts (moe.cu)
 int64_t moe_workspace_bytes(int T, int top, int experts, int width, int ff);
 bool moe_tc_supported(int width, int ff);
 // logits_ws ([T][experts] fp32) given and bf16 rows: the logits come from the tcgen05 linear (lin_ws: its split-K workspace)
+// sigmoid_scores: every expert's score is the sigmoid of its logit (no softmax over the experts)
 int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
               int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s, float* logits_ws = nullptr,
-              void* lin_ws = nullptr, int64_t lin_ws_bytes = 0);
+              void* lin_ws = nullptr, int64_t lin_ws_bytes = 0, bool sigmoid_scores = false);
+// The shape of an expert: gated = down(act(gate x) * (up x)) over [expert][2 ff][width], else down(act(up x)) over
+// [expert][ff][width]; weight_input: the mixing weight scales the expert's input row instead of its output row.
+struct ExpertForm {
+  bool gated = true;
+  int act = B200_ACT_SILU;
+  bool weight_input = false;
+};
 int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
-                const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s);
+                const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s,
+                ExpertForm form = ExpertForm());
+// ---- the parallel layer form (stream_ops.cu, latent.cu, mlstm.cu) ------------------------------------------------------------
+int seq_bounds(const int32_t* row_to_seq, int T, int S, int32_t* seq_start, cudaStream_t s);
+int embed_bigram(const int32_t* ids, const __nv_bfloat16* table, const __nv_bfloat16* bigram, float* out, int T, int width, int vocab,
+                 float scale, const int32_t* prev, int n_prev, const int32_t* positions, const int32_t* row_to_seq,
+                 const int32_t* seq_slots, const int32_t* state_prev, int64_t slot_stride_ints, int buckets, int mul_prev, int mul_cur,
+                 cudaStream_t s);
+int prev_token_commit(const int32_t* ids, int vocab, const int32_t* prev, int n_prev, const int32_t* seq_start, const int32_t* seq_slots,
+                      int S, int32_t* state_prev, int64_t slot_stride_ints, cudaStream_t s);
+int parallel_close(bool f32, float* u, const void* y_mix, const void* y_ff, const float* parts, int n_parts, const void* y_sh,
+                   float* results, int64_t result_stride, int n_results, const float* dwa, const float* g1, const float* g2,
+                   float* h1_f32, void* h1_act, void* h2, int T, int width, float eps, cudaStream_t s);
+int canon_conv(bool f32, const float* h, const float* w, void* out, int T, int width, int taps, const int32_t* positions,
+               const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots, float* tails, int64_t slot_stride,
+               cudaStream_t s);
+int rms_rows(bool f32, const float* u, const int32_t* rows, const float* g, void* out, int R, int width, float eps, cudaStream_t s);
+int ff_act(bool f32, const void* in, void* out, int T, int ff, bool gated, int kind, cudaStream_t s);
+int logit_cap(const float* in, float* out_f32, __nv_bfloat16* out_bf16, int R, int vocab, int ld, float cap, cudaStream_t s);
+int latent_prep(bool f32, const void* qkv, int64_t ld, const float* norm_w, const int32_t* positions, const int32_t* slots,
+                const float* rot, int rot_dims, int64_t max_pos, float* qfull, void* cache, int T, int heads, int dim, int rot_dim,
+                int kv_rank, float eps, cudaStream_t s);
+int head_linear(bool f32, bool y_f32, const void* x, int64_t ldx, int x_hs, const __nv_bfloat16* w, void* y, int64_t ldy, int y_hs,
+                const void* gate, int64_t ldg, int g_hs, int T, int heads, int n_out, int k, cudaStream_t s);
+int mlstm_gates(bool f32, const void* x, const __nv_bfloat16* w, const float* bias, float* out, int T, int width, int heads, float cap,
+                cudaStream_t s);
+int mlstm_col_blocks(int vd);
+int64_t mlstm_state_floats(int heads, int dim, int vd);
+int mlstm_scan(bool f32, const void* qkv, int64_t ld, int q_off, int k_off, int v_off, const float* gates, const int32_t* positions,
+               const int32_t* seq_start, const int32_t* seq_slots, float* state, int64_t slot_stride, float* out, int S, int heads,
+               int dim, int vd, cudaStream_t s);
+int head_norm_gate(bool f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int T, int heads, int vd, float eps,
+                   cudaStream_t s);
 // true-fp32 CUDA-core linear (linear_simt.cu)
 int linear_simt(bool x_f32, bool y_f32, const void* x, int64_t ldx, const __nv_bfloat16* w, void* y, int64_t ldy, int T, int n_out,
                 int k, cudaStream_t s);

@@ -97,11 +97,15 @@ struct StepArgs {
   // host-buffer entry: the tokens the previous step left in the ctx; an id -(j+1) means "row j of those"
   const int32_t* prev_tokens = nullptr;
   int n_prev = 0;
+  // models with per-sequence state: the state slot of each of the step's n_seqs sequences (host-buffer entry)
+  const int32_t* seq_slots = nullptr;
 };
 
 namespace b200 {
 // stack.cu: the step and readiness check of a layer-list model, and its teardown
 int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s);
 int stack_ready(const b200_ctx* c);
+int stack_state_slots(const b200_ctx* c);
+void stack_step_slots(const b200_ctx* c, const int32_t** seq_slots, int* n_seqs);   // what b200_stack_set_step_slots left   // > 0: the host-buffer step carries seq_slots behind its block tables
 void stack_destroy(b200_ctx* c);
 }  // namespace b200

@@ -48,18 +48,26 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 // One warp: softmax over the logits in sc[experts] (replaced by the scores), choice scores in ch, the group limit, top-k.
 __device__ __forceinline__ void route_select(float* sc, float* ch, float* gs, const float* __restrict__ bias, int lane, int t,
                                              int experts, int top, int groups, int keep, int32_t* __restrict__ out_ids,
-                                             float* __restrict__ out_w) {
-  float mx = -INFINITY;
-  for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, sc[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < experts; e += 32) sum += expf(sc[e] - mx);
-  sum = warp_sum(sum);
-  const float inv = 1.0f / sum;
-  for (int e = lane; e < experts; e += 32) {
-    const float s = expf(sc[e] - mx) * inv;
-    sc[e] = s;
-    ch[e] = s + (bias ? bias[e] : 0.f);
+                                             float* __restrict__ out_w, int sigmoid_scores) {
+  if (sigmoid_scores) {   // every expert scored on its own
+    for (int e = lane; e < experts; e += 32) {
+      const float s = 1.0f / (1.0f + expf(-sc[e]));
+      sc[e] = s;
+      ch[e] = s + (bias ? bias[e] : 0.f);
+    }
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, sc[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) sum += expf(sc[e] - mx);
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < experts; e += 32) {
+      const float s = expf(sc[e] - mx) * inv;
+      sc[e] = s;
+      ch[e] = s + (bias ? bias[e] : 0.f);
+    }
   }
   __syncwarp();
   if (groups > 1 && keep < groups) {
@@ -119,7 +127,7 @@ __device__ __forceinline__ void route_select(float* sc, float* ch, float* gs, co
 constexpr int kSelWarps = 4;
 __global__ void __launch_bounds__(kSelWarps * 32)
 moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int experts, int top, int groups,
-                  int keep, int32_t* __restrict__ out_ids, float* __restrict__ out_w) {
+                  int keep, int32_t* __restrict__ out_ids, float* __restrict__ out_w, int sigmoid_scores) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_launch_dependents();
@@ -131,16 +139,17 @@ moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ bi
   float* gs = ch + experts;
   for (int e = lane; e < experts; e += 32) sc[e] = logits[(int64_t)t * experts + e];
   __syncwarp();
-  route_select(sc, ch, gs, bias, lane, t, experts, top, groups, keep, out_ids, out_w);
+  route_select(sc, ch, gs, bias, lane, t, experts, top, groups, keep, out_ids, out_w, sigmoid_scores);
 }
 
 template <typename AT>
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ wr, const float* __restrict__ bias, int width,
-                 int experts, int top, int groups, int keep, int32_t* __restrict__ out_ids, float* __restrict__ out_w) {
+                 int experts, int top, int groups, int keep, int32_t* __restrict__ out_ids, float* __restrict__ out_w,
+                 int sigmoid_scores) {
   extern __shared__ float sm[];
   float* xs = sm;                 // [width]
-  float* sc = xs + width;         // [experts] softmax scores
+  float* sc = xs + width;         // [experts] scores
   float* ch = sc + experts;       // [experts] choice scores (eligible) / -inf
   float* gs = ch + experts;       // [groups]
   pdl_wait();
@@ -157,7 +166,7 @@ moe_route_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
   }
   __syncthreads();
   if (warp != 0) return;
-  route_select(sc, ch, gs, bias, lane, t, experts, top, groups, keep, out_ids, out_w);
+  route_select(sc, ch, gs, bias, lane, t, experts, top, groups, keep, out_ids, out_w, sigmoid_scores);
 }
 
 // ---- token form ---------------------------------------------------------------------------------------------------------
@@ -167,7 +176,7 @@ template <typename AT>
 __global__ void __launch_bounds__(kExpThreads)
 moe_expert_rows_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu, const __nv_bfloat16* __restrict__ w_down,
                        const int32_t* __restrict__ ids, const float* __restrict__ wts, int width, int ff, int top,
-                       float* __restrict__ parts) {
+                       float* __restrict__ parts, ExpertForm form) {
   extern __shared__ float sm[];
   float* xs = sm;            // [width]
   float* as = xs + width;    // [ff]
@@ -177,22 +186,28 @@ moe_expert_rows_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = kExpThreads / 32;
   const int e = ids[(int64_t)t * top + slot];
   const float wt = wts[(int64_t)t * top + slot];
-  for (int c = threadIdx.x; c < width; c += kExpThreads) xs[c] = ld_act<AT>(x, (int64_t)t * width + c);
+  const float w_in = form.weight_input ? wt : 1.0f, w_out = form.weight_input ? 1.0f : wt;
+  for (int c = threadIdx.x; c < width; c += kExpThreads) xs[c] = ld_act<AT>(x, (int64_t)t * width + c) * w_in;
   __syncthreads();
-  const __nv_bfloat16* wg = w_gu + (int64_t)e * 2 * ff * width;
+  const __nv_bfloat16* wg = w_gu + (int64_t)e * (form.gated ? 2 : 1) * ff * width;
   const __nv_bfloat16* wu = wg + (int64_t)ff * width;
   for (int f = warp; f < ff; f += nw) {
     const __nv_bfloat16* g = wg + (int64_t)f * width;
     const __nv_bfloat16* u = wu + (int64_t)f * width;
     float a = 0.f, b = 0.f;
-    for (int c = lane; c < width; c += 32) {
-      const float xv = xs[c];
-      a = fmaf(__bfloat162float(g[c]), xv, a);
-      b = fmaf(__bfloat162float(u[c]), xv, b);
+    if (form.gated) {
+      for (int c = lane; c < width; c += 32) {
+        const float xv = xs[c];
+        a = fmaf(__bfloat162float(g[c]), xv, a);
+        b = fmaf(__bfloat162float(u[c]), xv, b);
+      }
+      b = warp_sum(b);
+    } else {
+      for (int c = lane; c < width; c += 32) a = fmaf(__bfloat162float(g[c]), xs[c], a);
+      b = 1.0f;
     }
     a = warp_sum(a);
-    b = warp_sum(b);
-    if (lane == 0) as[f] = a / (1.0f + expf(-a)) * b;
+    if (lane == 0) as[f] = act_apply(a, form.act) * b;
   }
   __syncthreads();
   const __nv_bfloat16* wd = w_down + (int64_t)e * width * ff;
@@ -202,7 +217,7 @@ moe_expert_rows_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict
     float a = 0.f;
     for (int c = lane; c < ff; c += 32) a = fmaf(__bfloat162float(d[c]), as[c], a);
     a = warp_sum(a);
-    if (lane == 0) dst[o] = a * wt;
+    if (lane == 0) dst[o] = a * w_out;
   }
 }
 
@@ -244,7 +259,7 @@ template <typename AT>
 __global__ void __launch_bounds__(kExpThreads)
 moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu, const __nv_bfloat16* __restrict__ w_down,
                           const int32_t* __restrict__ offsets, const int32_t* __restrict__ list, const float* __restrict__ wts,
-                          int width, int ff, int top, float* __restrict__ parts) {
+                          int width, int ff, int top, float* __restrict__ parts, ExpertForm form) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_launch_dependents();
@@ -260,11 +275,11 @@ moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restr
   __syncthreads();
   for (int i = threadIdx.x; i < kGrpTokens * width; i += kExpThreads) {
     const int r = i / width, c = i % width;
-    xs[i] = r < n ? ld_act<AT>(x, (int64_t)(pair_of[r] / top) * width + c) : 0.f;
+    xs[i] = r < n ? ld_act<AT>(x, (int64_t)(pair_of[r] / top) * width + c) * (form.weight_input ? wts[pair_of[r]] : 1.0f) : 0.f;
   }
   __syncthreads();
-  const __nv_bfloat16* wg = w_gu + (int64_t)e * 2 * ff * width;
-  const __nv_bfloat16* wu = wg + (int64_t)ff * width;
+  const __nv_bfloat16* wg = w_gu + (int64_t)e * (form.gated ? 2 : 1) * ff * width;
+  const __nv_bfloat16* wu = form.gated ? wg + (int64_t)ff * width : wg;
   for (int f = warp; f < ff; f += nw) {
     const __nv_bfloat16* g = wg + (int64_t)f * width;
     const __nv_bfloat16* u = wu + (int64_t)f * width;
@@ -283,7 +298,7 @@ moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restr
 #pragma unroll
     for (int r = 0; r < kGrpTokens; ++r) {
       const float av = warp_sum(a[r]), bv = warp_sum(b[r]);
-      if (lane == 0) as[r * ff + f] = av / (1.0f + expf(-av)) * bv;
+      if (lane == 0) as[r * ff + f] = act_apply(av, form.act) * (form.gated ? bv : 1.0f);
     }
   }
   __syncthreads();
@@ -301,7 +316,7 @@ moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restr
 #pragma unroll
     for (int r = 0; r < kGrpTokens; ++r) {
       const float av = warp_sum(a[r]);
-      if (lane == 0 && r < n) parts[(int64_t)pair_of[r] * width + o] = av * wts[pair_of[r]];
+      if (lane == 0 && r < n) parts[(int64_t)pair_of[r] * width + o] = form.weight_input ? av : av * wts[pair_of[r]];
     }
   }
 }
@@ -475,7 +490,8 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
 
 int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
               int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s, float* logits_ws, void* lin_ws,
-              int64_t lin_ws_bytes) {
+              int64_t lin_ws_bytes, bool sigmoid_scores) {
+  const int sg = sigmoid_scores ? 1 : 0;
   if (T == 0) return B200_OK;
   B200_REQUIRE(experts > 0 && top > 0 && top <= experts, B200_ERR_INVALID, "router: top %d of %d experts", top, experts);
   if (groups < 1) groups = 1;
@@ -494,7 +510,7 @@ int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const floa
                              lin_ws_bytes, &ex, s);
     if (rc) return rc;
     B200_CUDA(launch(moe_select_kernel, dim3((T + kSelWarps - 1) / kSelWarps), dim3(kSelWarps * 32), smem_sel, s,
-                     (const float*)logits_ws, bias, T, experts, top, groups, keep, out_ids, out_w));
+                     (const float*)logits_ws, bias, T, experts, top, groups, keep, out_ids, out_w, sg));
     return B200_OK;
   }
   const size_t smem = ((size_t)width + 2 * experts + groups) * 4;
@@ -503,18 +519,19 @@ int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const floa
   if (f32) {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(moe_route_kernel<float>, 200 * 1024, done[0]));
     B200_CUDA(launch(moe_route_kernel<float>, dim3(T), dim3(kRouteThreads), smem, s, (const float*)x, w_router, bias, width, experts,
-                     top, groups, keep, out_ids, out_w));
+                     top, groups, keep, out_ids, out_w, sg));
   } else {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(moe_route_kernel<__nv_bfloat16>, 200 * 1024, done[1]));
     B200_CUDA(launch(moe_route_kernel<__nv_bfloat16>, dim3(T), dim3(kRouteThreads), smem, s, (const __nv_bfloat16*)x, w_router,
-                     bias, width, experts, top, groups, keep, out_ids, out_w));
+                     bias, width, experts, top, groups, keep, out_ids, out_w, sg));
   }
   return B200_OK;
 }
 
 template <typename AT>
 static int moe_experts_t(const AT* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids, const float* wts,
-                         int T, int width, int ff, int experts, int top, float* parts, void* ws, bool grouped, cudaStream_t s) {
+                         int T, int width, int ff, int experts, int top, float* parts, void* ws, bool grouped, cudaStream_t s,
+                         ExpertForm form) {
   const size_t smem_g = (size_t)kGrpTokens * (width + ff) * 4;
   if (grouped && ws != nullptr && smem_g <= 200 * 1024) {
     int32_t* offsets = static_cast<int32_t*>(ws);
@@ -525,7 +542,7 @@ static int moe_experts_t(const AT* x, const __nv_bfloat16* w_gu, const __nv_bflo
     const int tiles = (T * top + kGrpTokens - 1) / kGrpTokens;   // upper bound of any expert's tiles
     B200_CUDA(launch(moe_expert_grouped_kernel<AT>, dim3(std::min(tiles, (T + kGrpTokens - 1) / kGrpTokens + 1), experts),
                      dim3(kExpThreads), smem_g, s, x, w_gu, w_down, (const int32_t*)offsets, (const int32_t*)list, wts, width, ff,
-                     top, parts));
+                     top, parts, form));
     return B200_OK;
   }
   const size_t smem = ((size_t)width + ff) * 4;
@@ -533,22 +550,24 @@ static int moe_experts_t(const AT* x, const __nv_bfloat16* w_gu, const __nv_bflo
   static bool done2[64] = {};
   if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(moe_expert_rows_kernel<AT>, 200 * 1024, done2));
   B200_CUDA(launch(moe_expert_rows_kernel<AT>, dim3(T, top), dim3(kExpThreads), smem, s, x, w_gu, w_down, ids, wts, width, ff, top,
-                   parts));
+                   parts, form));
   return B200_OK;
 }
 
 // parts [T][top][width] fp32: the chosen experts' outputs times their mixing weights, one row per (token, slot).
 int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
-                const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s) {
+                const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s,
+                ExpertForm form) {
   if (T == 0) return B200_OK;
   static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
-  if (!f32 && tc_env && ws && moe_tc_supported(width, ff))
+  const bool first_form = form.gated && form.act == B200_ACT_SILU && !form.weight_input;
+  if (!f32 && tc_env && ws && moe_tc_supported(width, ff) && first_form)
     return moe_experts_tc((const __nv_bfloat16*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, s);
   // an expert is chosen at most once per token, so it has at most T tokens: ceil(T / 16) tiles bound every expert
   const bool grouped = (int64_t)T * top >= 4 * (int64_t)experts && T >= 64;
-  return f32 ? moe_experts_t<float>((const float*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, grouped, s)
+  return f32 ? moe_experts_t<float>((const float*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, grouped, s, form)
              : moe_experts_t<__nv_bfloat16>((const __nv_bfloat16*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts,
-                                            ws, grouped, s);
+                                            ws, grouped, s, form);
 }
 
 }  // namespace b200

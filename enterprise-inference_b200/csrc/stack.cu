@@ -10,6 +10,14 @@
 //               x += LN(y); h = LN(x)            one kernel (sandwich norm)
 //               router -> chosen experts -> per-slot partial rows;  x += LN(sum of slots); h = LN(x) for the next layer
 //   logit rows: LN(x[rows]) -> W_head -> logits (bf16 for the samplers; fp32 mode keeps the unrounded rows too) -> argmax
+//
+// Parallel form (b200_stack_cfg.form = B200_FORM_PARALLEL), same step entry, cache and graph replay:
+//   X_0 = table[id] * embed_scale + bigram row                            fp32; u = X_0
+//   per layer:  h1 = u / rms(u) * g1, h2 = u / rms(u) * g2  ->  hc = h1 + conv(h1) (tail in the state slot)
+//               mixer(hc): latent attention over the paged cache of [latent | rotated key part] rows, or the mLSTM
+//               recurrence over the state slot;  ff(h2): dense gated, or routed experts + shared expert
+//               X_{i+1} = u + (mixer + ff);  u = sum_j dwa[j] X_j;  norms of the next layer      one kernel
+//   logit rows: u[rows] / rms * g -> W_head -> fp32 logits -> soft cap -> fp32 and bf16 copies -> argmax
 #include <math.h>
 #include <stdlib.h>
 
@@ -26,6 +34,11 @@ struct StackLayerW {
               *k_norm = nullptr, *router_bias = nullptr;
   const __nv_bfloat16 *qkv = nullptr, *o = nullptr, *router = nullptr, *e_gate_up = nullptr, *e_down = nullptr;
   void *kc = nullptr, *vc = nullptr;
+  // parallel form
+  const float *canon = nullptr, *dwa = nullptr, *sink = nullptr, *gates_bias = nullptr, *head_norm = nullptr;
+  const __nv_bfloat16 *uk_t = nullptr, *uv = nullptr, *gates = nullptr, *mlp_gate_up = nullptr, *mlp_down = nullptr,
+                      *shared_up = nullptr, *shared_down = nullptr;
+  int64_t tail_off = 0, rec_off = 0;   // floats from the start of a state slot: convolution tail, recurrent state
 };
 
 struct StackModel {
@@ -50,9 +63,21 @@ struct StackModel {
   void* attn_tc_ws = nullptr;   // row plan and split partials of the 128-wide tensor-core attention kernels
   int64_t attn_tc_ws_bytes = 0;
   float* tap = nullptr;
+  // parallel form
+  const __nv_bfloat16* bigram = nullptr;
+  float* state = nullptr;              // caller-owned, n_state_slots slots of slot_floats floats
+  int64_t slot_floats = 0;
+  const int32_t* step_slots = nullptr; // device-pointer steps: the slots of the step's sequences
+  int step_seqs = 0;
+  float *results = nullptr, *h1f = nullptr, *gates_buf = nullptr, *oraw = nullptr, *head_f32 = nullptr;
+  void *hc = nullptr, *lat = nullptr, *y2 = nullptr, *y3 = nullptr, *gu = nullptr, *ffa = nullptr;
+  int32_t* seq_start = nullptr;
 };
 
 bool paged_attn_tc_supported(int hq, int hkv, int block_size);   // attn_tc.cu
+
+static bool is_latent(const b200_stack_layer& L) { return L.mixer == B200_MIXER_LATENT; }
+static bool is_mlstm(const b200_stack_layer& L) { return L.mixer == B200_MIXER_MLSTM; }
 
 // bf16 mode, keys and values of 64 to 128 dimensions in blocks of 128 tokens: the tcgen05 attention kernels of the fixed
 // decoder stack serve the layer.  They are built for 128-wide heads, so the layer's cache rows and its bf16 queries are
@@ -60,15 +85,29 @@ bool paged_attn_tc_supported(int hq, int hkv, int block_size);   // attn_tc.cu
 // packing of narrower value heads are a step of their own.  Every other shape takes attn_anydim.cu.
 static bool layer_attn_tc(const b200_stack_cfg& m, const b200_stack_layer& L) {
   static const int env = getenv("B200_STACK_ATTN_TC") ? atoi(getenv("B200_STACK_ATTN_TC")) : 1;
-  return env && !m.f32 && L.dim >= kHeadDim / 2 && L.dim <= kHeadDim && L.vdim >= kHeadDim / 2 && L.vdim <= kHeadDim &&
+  return env && L.mixer == B200_MIXER_ATTENTION && !m.f32 && L.dim >= kHeadDim / 2 && L.dim <= kHeadDim && L.vdim >= kHeadDim / 2 && L.vdim <= kHeadDim &&
          L.scale > 0.f && paged_attn_tc_supported(L.heads, L.kv_heads, m.block_size);
 }
-static int cache_kdim(const b200_stack_cfg& m, const b200_stack_layer& L) { return layer_attn_tc(m, L) ? kHeadDim : L.dim; }
-static int cache_vdim(const b200_stack_cfg& m, const b200_stack_layer& L) { return layer_attn_tc(m, L) ? kHeadDim : L.vdim; }
+// latent mixers cache one row [latent | rotated key part] per token (no value cache); mLSTM layers cache nothing
+static int cache_kdim(const b200_stack_cfg& m, const b200_stack_layer& L) {
+  if (is_latent(L)) return L.kv_rank + L.rot_dim;
+  if (is_mlstm(L)) return 0;
+  return layer_attn_tc(m, L) ? kHeadDim : L.dim;
+}
+static int cache_vdim(const b200_stack_cfg& m, const b200_stack_layer& L) {
+  if (is_latent(L) || is_mlstm(L)) return 0;
+  return layer_attn_tc(m, L) ? kHeadDim : L.vdim;
+}
 
 static int64_t up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
-static int qkv_rows(const b200_stack_layer& L) { return L.heads * L.dim + L.kv_heads * (L.dim + L.vdim); }
+// rows of the fused projection of the mixer's input
+static int qkv_rows(const b200_stack_layer& L) {
+  if (is_latent(L))
+    return L.heads * (L.dim + L.rot_dim) + L.kv_rank + L.rot_dim + ((L.mixer_flags & B200_MIXF_GATE) ? L.heads * L.vdim : 0);
+  if (is_mlstm(L)) return 2 * L.heads * L.dim + 2 * L.heads * L.vdim;
+  return L.heads * L.dim + L.kv_heads * (L.dim + L.vdim);
+}
 
 // bf16 mode: the tcgen05 weight-streaming linear wherever TMA can address the operands, else the CUDA-core tile kernel;
 // fp32 mode: the CUDA-core kernel in true fp32.
@@ -84,9 +123,40 @@ static int stack_linear(b200_ctx* c, const void* x, int64_t ldx, const __nv_bflo
   return linear_simt(false, false, x, ldx, w, y, ldy, T, n_out, k, s);
 }
 
+static int stack_ready_parallel(const b200_ctx* c) {
+  const StackModel* M = c->stack;
+  const b200_stack_cfg& m = M->cfg;
+  B200_REQUIRE(m.bigram_buckets <= 0 || M->bigram, B200_ERR_STATE, "step: bigram table not set");
+  B200_REQUIRE(m.n_state_slots <= 0 || M->state, B200_ERR_STATE, "step: state slots not set");
+  for (size_t l = 0; l < M->layers.size(); ++l) {
+    const b200_stack_layer& L = M->layers[l];
+    const StackLayerW& W = M->w[l];
+    const int li = (int)l;
+    B200_REQUIRE(W.n_mix_pre && W.qkv && W.o, B200_ERR_STATE, "step: layer %d mixer weights incomplete", li);
+    B200_REQUIRE(m.canon_taps <= 0 || W.canon, B200_ERR_STATE, "step: layer %d convolution weights missing", li);
+    B200_REQUIRE(!m.depth_avg || W.dwa, B200_ERR_STATE, "step: layer %d depth-average weights missing", li);
+    if (is_latent(L)) {
+      B200_REQUIRE(W.k_norm && W.uk_t && W.uv && W.kc, B200_ERR_STATE, "step: layer %d latent weights / cache incomplete", li);
+      B200_REQUIRE(!(L.mixer_flags & B200_MIXF_SINK) || W.sink, B200_ERR_STATE, "step: layer %d sink missing", li);
+      B200_REQUIRE(L.rot_dims == 0 || (L.rot_table >= 0 && M->rot[L.rot_table] && M->rot_half[L.rot_table] * 2 == L.rot_dims),
+                   B200_ERR_STATE, "step: layer %d rotation table missing or of another size", li);
+    } else {
+      B200_REQUIRE(W.gates && W.head_norm, B200_ERR_STATE, "step: layer %d recurrent weights incomplete", li);
+    }
+    if (L.mlp != B200_MLP_NONE) B200_REQUIRE(W.n_mlp_pre, B200_ERR_STATE, "step: layer %d second norm missing", li);
+    if (L.mlp == B200_MLP_DENSE) B200_REQUIRE(W.mlp_gate_up && W.mlp_down, B200_ERR_STATE, "step: layer %d feed-forward weights incomplete", li);
+    if (L.mlp == B200_MLP_MOE) {
+      B200_REQUIRE(W.router && W.e_gate_up && W.e_down, B200_ERR_STATE, "step: layer %d expert weights incomplete", li);
+      B200_REQUIRE(L.shared_ff <= 0 || (W.shared_up && W.shared_down), B200_ERR_STATE, "step: layer %d shared expert incomplete", li);
+    }
+  }
+  return B200_OK;
+}
+
 int stack_ready(const b200_ctx* c) {
   const StackModel* M = c->stack;
   B200_REQUIRE(M->embed && M->head && M->final_norm, B200_ERR_STATE, "step: embedding / output weights not set");
+  if (M->cfg.form == B200_FORM_PARALLEL) return stack_ready_parallel(c);
   for (size_t l = 0; l < M->layers.size(); ++l) {
     const b200_stack_layer& L = M->layers[l];
     const StackLayerW& W = M->w[l];
@@ -103,14 +173,150 @@ int stack_ready(const b200_ctx* c) {
   return B200_OK;
 }
 
+int stack_state_slots(const b200_ctx* c) { return c->stack ? c->stack->cfg.n_state_slots : 0; }
+
+void stack_step_slots(const b200_ctx* c, const int32_t** seq_slots, int* n_seqs) {
+  *seq_slots = c->stack->step_slots;
+  *n_seqs = c->stack->step_seqs;
+}
+
 void stack_destroy(b200_ctx* c) {
   delete c->stack;
   c->stack = nullptr;
 }
 
+// The step of the parallel form.  Sequences of the step: a.n_seqs with their slots behind the block tables (host-buffer
+// entry), or the array given by b200_stack_set_step_slots (device-pointer entry).
+static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
+  StackModel* M = c->stack;
+  const b200_stack_cfg& m = M->cfg;
+  const bool f32 = m.f32 != 0;
+  const int T = a.T, Wd = m.width, nL = m.n_layers;
+  const int64_t es = M->esz;
+  int rc;
+#define STEP(expr)     \
+  do {                 \
+    rc = (expr);       \
+    if (rc) return rc; \
+  } while (0)
+  const bool stateful = m.n_state_slots > 0;
+  const int S = a.n_seqs > 0 ? a.n_seqs : T;
+  const int32_t* seq_slots = a.seq_slots;
+  B200_REQUIRE(!stateful || seq_slots, B200_ERR_STATE, "step: the state slots of the step's sequences were not given");
+  B200_REQUIRE(S <= T, B200_ERR_INVALID, "step: %d sequences in %d rows", S, T);
+  int attn_plan = (a.row_to_seq && T >= 32 && T >= 2 * S) ? 1 : 0;
+  static const int plan_env = getenv("B200_STACK_ATTN_RUNS") ? atoi(getenv("B200_STACK_ATTN_RUNS")) : 1;
+  if (!plan_env) attn_plan = 0;
+  const int64_t rstride = (int64_t)m.max_tokens * Wd;
+  float* u = M->x;
+  int32_t* st_prev = reinterpret_cast<int32_t*>(M->state);
+  STEP(seq_bounds(a.row_to_seq, T, S, M->seq_start, s));
+  STEP(embed_bigram(a.ids, M->embed, M->bigram, u, T, Wd, m.vocab, m.embed_scale, a.prev_tokens, a.n_prev, a.positions, a.row_to_seq,
+                    seq_slots, stateful ? st_prev : nullptr, M->slot_floats, m.bigram_buckets, m.bigram_mul_prev, m.bigram_mul_cur, s));
+  if (stateful && m.bigram_buckets > 0)
+    STEP(prev_token_commit(a.ids, m.vocab, a.prev_tokens, a.n_prev, M->seq_start, seq_slots, S, st_prev, M->slot_floats, s));
+  const bool conv = m.canon_taps > 1;
+  // X_0 and the first layer's norms
+  STEP(parallel_close(f32, u, nullptr, nullptr, nullptr, 0, nullptr, m.depth_avg ? M->results : nullptr, rstride, 1, nullptr,
+                      M->w[0].n_mix_pre, M->w[0].n_mlp_pre, conv ? M->h1f : nullptr, conv ? nullptr : M->hc, M->hn, T, Wd, m.norm_eps, s));
+  for (int l = 0; l < nL; ++l) {
+    const b200_stack_layer& L = M->layers[l];
+    const StackLayerW& W = M->w[l];
+    const int qr = qkv_rows(L);
+    if (conv)
+      STEP(canon_conv(f32, M->h1f, W.canon, M->hc, T, Wd, m.canon_taps, a.positions, a.row_to_seq, M->seq_start, seq_slots,
+                      M->state + W.tail_off, M->slot_floats, s));
+    STEP(stack_linear(c, M->hc, Wd, W.qkv, M->qkv, qr, T, qr, Wd, s));
+    const int av = L.heads * L.vdim;
+    if (is_latent(L)) {
+      const int qh = L.dim + L.rot_dim, krow = L.kv_rank + L.rot_dim;
+      const float* rot = L.rot_dims > 0 ? M->rot[L.rot_table] : nullptr;
+      const int64_t max_pos = rot ? M->rot_pos[L.rot_table] : (1ll << 40);
+      STEP(latent_prep(f32, M->qkv, qr, W.k_norm, a.positions, a.slots, rot, L.rot_dims, max_pos, M->q, W.kc, T, L.heads, L.dim,
+                       L.rot_dim, L.kv_rank, m.norm_eps, s));
+      // q' = W_uk^T q_plain into the leading kv_rank entries of every query row
+      STEP(head_linear(f32, true, M->qkv, qr, qh, W.uk_t, M->q, (int64_t)L.heads * krow, krow, nullptr, 0, 0, T, L.heads, L.kv_rank,
+                       L.dim, s));
+      STEP(paged_attn_anydim(f32, M->q, W.kc, W.kc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
+                             M->lat, T, L.heads, 1, krow, L.kv_rank, m.block_size, L.scale, attn_plan, M->attn_ws, s, krow, krow,
+                             (L.mixer_flags & B200_MIXF_SINK) ? W.sink : nullptr));
+      if (attn_plan == 1) attn_plan = 2;
+      const bool gate = (L.mixer_flags & B200_MIXF_GATE) != 0;
+      const char* gptr = static_cast<const char*>(M->qkv) + (int64_t)(L.heads * qh + krow) * es;
+      STEP(head_linear(f32, false, M->lat, (int64_t)L.heads * L.kv_rank, L.kv_rank, W.uv, M->attn, av, L.vdim, gate ? gptr : nullptr, qr,
+                       L.vdim, T, L.heads, L.vdim, L.kv_rank, s));
+    } else {
+      const int hd = L.heads * L.dim;
+      STEP(mlstm_gates(f32, M->hc, W.gates, W.gates_bias, M->gates_buf, T, Wd, L.heads, L.gate_cap, s));
+      STEP(mlstm_scan(f32, M->qkv, qr, 0, hd, 2 * hd, M->gates_buf, a.positions, M->seq_start, seq_slots, M->state + W.rec_off,
+                      M->slot_floats, M->oraw, S, L.heads, L.dim, L.vdim, s));
+      const char* gptr = static_cast<const char*>(M->qkv) + (int64_t)(2 * hd + av) * es;
+      STEP(head_norm_gate(f32, M->oraw, W.head_norm, gptr, qr, M->attn, T, L.heads, L.vdim, m.norm_eps, s));
+    }
+    STEP(stack_linear(c, M->attn, av, W.o, M->y, Wd, T, Wd, av, s));
+    const void *y_ff = nullptr, *y_sh = nullptr;
+    const float* parts = nullptr;
+    int n_parts = 0;
+    if (L.mlp == B200_MLP_DENSE) {
+      STEP(stack_linear(c, M->hn, Wd, W.mlp_gate_up, M->gu, 2 * L.ff, T, 2 * L.ff, Wd, s));
+      STEP(ff_act(f32, M->gu, M->ffa, T, L.ff, true, L.act, s));
+      STEP(stack_linear(c, M->ffa, L.ff, W.mlp_down, M->y2, Wd, T, Wd, L.ff, s));
+      y_ff = M->y2;
+    } else if (L.mlp == B200_MLP_MOE) {
+      STEP(moe_route(f32, M->hn, W.router, W.router_bias, T, Wd, L.experts, L.top, L.groups, L.keep, M->route_ids, M->route_w, s,
+                     M->route_logits, c->lin_ws, c->lin_ws_bytes, L.sigmoid_scores != 0));
+      ExpertForm form;
+      form.gated = !L.ungated;
+      form.act = L.act;
+      form.weight_input = L.weight_input != 0;
+      STEP(moe_experts(f32, M->hn, W.e_gate_up, W.e_down, M->route_ids, M->route_w, T, Wd, L.ff, L.experts, L.top, M->parts, M->moe_ws,
+                       s, form));
+      parts = M->parts;
+      n_parts = L.top;
+      if (L.shared_ff > 0) {
+        const int sr = (L.ungated ? 1 : 2) * L.shared_ff;
+        STEP(stack_linear(c, M->hn, Wd, W.shared_up, M->gu, sr, T, sr, Wd, s));
+        STEP(ff_act(f32, M->gu, M->ffa, T, L.shared_ff, !L.ungated, L.act, s));
+        STEP(stack_linear(c, M->ffa, L.shared_ff, W.shared_down, M->y3, Wd, T, Wd, L.shared_ff, s));
+        y_sh = M->y3;
+      }
+    }
+    const bool last = l + 1 == nL;
+    STEP(parallel_close(f32, u, M->y, y_ff, parts, n_parts, y_sh, m.depth_avg ? M->results : nullptr, rstride, l + 2,
+                        m.depth_avg ? W.dwa : nullptr, last ? nullptr : M->w[l + 1].n_mix_pre, last ? nullptr : M->w[l + 1].n_mlp_pre,
+                        conv ? M->h1f : nullptr, conv ? nullptr : M->hc, M->hn, T, Wd, m.norm_eps, s));
+    if (M->tap) B200_CUDA(cudaMemcpyAsync(M->tap + (int64_t)l * T * Wd, u, (size_t)T * Wd * 4, cudaMemcpyDeviceToDevice, s));
+  }
+  STEP(rms_rows(f32, u, a.logit_rows, M->final_norm, M->lm_in, a.R, Wd, m.norm_eps, s));
+  if (f32) {
+    STEP(linear_simt(true, true, M->lm_in, Wd, M->head, M->head_f32, m.vocab, a.R, m.vocab, Wd, s));
+  } else {
+    // unrounded fp32 rows from the tcgen05 linear where it can address the operands, else the CUDA-core linear
+    static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
+    if (tc_env && Wd % 8 == 0 && reinterpret_cast<uintptr_t>(M->head) % 16 == 0 && linear_tc_supported(a.R, m.vocab, Wd) &&
+        linear_tc_workspace_bytes(a.R, m.vocab, Wd) <= c->lin_ws_bytes) {
+      LinearExtra ex;
+      ex.mode = 4;
+      ex.out_f32 = M->head_f32;
+      STEP(linear_tc((const __nv_bfloat16*)M->lm_in, Wd, M->head, nullptr, nullptr, m.vocab, a.R, m.vocab, Wd, c->lin_ws, c->lin_ws_bytes,
+                     &ex, s));
+    } else {
+      STEP(linear_simt(false, true, M->lm_in, Wd, M->head, M->head_f32, m.vocab, a.R, m.vocab, Wd, s));
+    }
+  }
+  STEP(logit_cap(M->head_f32, c->logits_f32, c->logits, a.R, m.vocab, c->logits_ld, m.logit_softcap, s));
+  STEP(argmax_rows(c->logits, c->logits_ld, a.R, m.vocab, 0, a.out_tokens, nullptr, s));
+  if (a.out_logits)
+    B200_CUDA(cudaMemcpy2DAsync(a.out_logits, (size_t)m.vocab * 2, c->logits, (size_t)c->logits_ld * 2, (size_t)m.vocab * 2, a.R,
+                                cudaMemcpyDeviceToDevice, s));
+#undef STEP
+  return B200_OK;
+}
+
 int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
   StackModel* M = c->stack;
   const b200_stack_cfg& m = M->cfg;
+  if (m.form == B200_FORM_PARALLEL) return stack_enqueue_step_parallel(c, a, s);
   const bool f32 = m.f32 != 0;
   const int T = a.T, Wd = m.width, nL = m.n_layers;
   int rc;
@@ -208,16 +414,35 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
   B200_REQUIRE(cfg->width > 0 && cfg->vocab > 0 && cfg->n_layers > 0 && cfg->block_size > 0 && cfg->max_tokens > 0 &&
                    cfg->max_blocks_per_seq > 0 && cfg->max_logit_rows > 0,
                B200_ERR_INVALID, "stack_create: bad sizes");
-  int max_qkv = 0, max_q = 0, max_a = 0, max_top = 0, max_exp = 0, max_ff = 0;
+  int max_qkv = 0, max_q = 0, max_a = 0, max_top = 0, max_exp = 0, max_ff = 0, max_lat = 0, max_gates = 0, max_gu = 0, max_ffa = 0;
   int64_t moe_ws_bytes = 16;
   for (int l = 0; l < cfg->n_layers; ++l) {
     const b200_stack_layer& L = layers[l];
+    if (cfg->form == B200_FORM_PARALLEL) {
+      B200_REQUIRE(L.mixer == B200_MIXER_LATENT || L.mixer == B200_MIXER_MLSTM, B200_ERR_UNSUPPORTED,
+                   "stack_create: layer %d: mixer %d is not served in the parallel form", l, L.mixer);
+      B200_REQUIRE(L.heads > 0 && L.dim > 0 && L.vdim > 0, B200_ERR_INVALID, "stack_create: layer %d: bad mixer sizes", l);
+      if (L.mixer == B200_MIXER_LATENT)
+        B200_REQUIRE(L.kv_rank > 0 && L.rot_dim >= 0 && L.rot_dims >= 0 && L.rot_dims <= L.rot_dim && L.rot_dims % 2 == 0 &&
+                         L.rot_table < 16 && L.kv_rank <= 512,
+                     B200_ERR_INVALID, "stack_create: layer %d: bad latent sizes", l);
+      else
+        B200_REQUIRE(L.gate_cap > 0.f && L.dim <= 256 && cfg->n_state_slots > 0, B200_ERR_INVALID,
+                     "stack_create: layer %d: bad recurrent sizes (or no state slots)", l);
+      B200_REQUIRE(L.mlp == B200_MLP_NONE || L.mlp == B200_MLP_MOE || L.mlp == B200_MLP_DENSE, B200_ERR_UNSUPPORTED,
+                   "stack_create: layer %d: unknown feed-forward %d", l, L.mlp);
+      B200_REQUIRE(L.mlp == B200_MLP_NONE || (L.ff > 0 && L.act >= 0 && L.act <= B200_ACT_RELU2 && L.shared_ff >= 0), B200_ERR_INVALID,
+                   "stack_create: layer %d: bad feed-forward sizes", l);
+    } else {
     B200_REQUIRE(L.mixer == B200_MIXER_ATTENTION, B200_ERR_UNSUPPORTED, "stack_create: layer %d: unknown mixer %d", l, L.mixer);
     B200_REQUIRE(L.heads > 0 && L.kv_heads > 0 && L.heads % L.kv_heads == 0 && L.dim > 0 && L.vdim > 0 && L.dim % 2 == 0 &&
                      L.rot_dims >= 0 && L.rot_dims <= L.dim && L.rot_dims % 2 == 0 && (L.vrot_table < 0 || L.vdim % 2 == 0) &&
                      L.rot_table < 16 && L.vrot_table < 16,
                  B200_ERR_INVALID, "stack_create: layer %d: bad attention sizes", l);
     B200_REQUIRE(L.mlp == B200_MLP_NONE || L.mlp == B200_MLP_MOE, B200_ERR_UNSUPPORTED, "stack_create: layer %d: unknown feed-forward %d", l, L.mlp);
+    B200_REQUIRE(!L.ungated && !L.sigmoid_scores && !L.weight_input && !L.shared_ff && L.act == B200_ACT_SILU, B200_ERR_UNSUPPORTED,
+                 "stack_create: layer %d: this feed-forward shape is served in the parallel form only", l);
+    }
     if (L.mlp == B200_MLP_MOE) {
       const int groups = L.groups < 1 ? 1 : L.groups;
       B200_REQUIRE(L.experts > 0 && L.top > 0 && L.top <= L.experts && L.ff > 0 && L.experts % groups == 0 && L.keep >= 1 &&
@@ -229,9 +454,19 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       moe_ws_bytes = std::max(moe_ws_bytes, moe_workspace_bytes(cfg->max_tokens, L.top, L.experts, cfg->f32 ? 0 : cfg->width, L.ff));
     }
     max_qkv = std::max(max_qkv, qkv_rows(L));
-    max_q = std::max(max_q, L.heads * L.dim);
+    max_q = std::max(max_q, L.heads * (is_latent(L) ? L.kv_rank + L.rot_dim : L.dim));
     max_a = std::max(max_a, L.heads * L.vdim);
+    if (is_latent(L)) max_lat = std::max(max_lat, L.heads * L.kv_rank);
+    if (is_mlstm(L)) max_gates = std::max(max_gates, 2 * L.heads);
+    if (L.mlp == B200_MLP_DENSE) max_gu = std::max(max_gu, 2 * L.ff), max_ffa = std::max(max_ffa, L.ff);
+    if (L.shared_ff > 0) max_gu = std::max(max_gu, 2 * L.shared_ff), max_ffa = std::max(max_ffa, L.shared_ff);
   }
+  const bool par = cfg->form == B200_FORM_PARALLEL;
+  B200_REQUIRE(par || (!cfg->canon_taps && !cfg->depth_avg && !cfg->bigram_buckets && cfg->logit_softcap == 0.f), B200_ERR_UNSUPPORTED,
+               "stack_create: convolution, depth average, bigram rows and the logit cap belong to the parallel form");
+  B200_REQUIRE(!par || ((cfg->canon_taps == 0 || (cfg->canon_taps >= 2 && cfg->canon_taps <= 8)) && cfg->n_state_slots >= 0 &&
+                        ((cfg->canon_taps == 0 && cfg->bigram_buckets <= 0) || cfg->n_state_slots > 0)),
+               B200_ERR_INVALID, "stack_create: bad convolution taps or no state slots");
   b200_ctx* c = new b200_ctx();
   StackModel* M = new StackModel();
   c->stack = M;
@@ -239,6 +474,22 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
   M->layers.assign(layers, layers + cfg->n_layers);
   M->w.resize(cfg->n_layers);
   M->esz = cfg->f32 ? 4 : 2;
+  if (par && cfg->n_state_slots > 0) {
+    // one slot: [previous token (int32) + padding to 4 floats | per layer: convolution tail [taps - 1][width], recurrent state]
+    int64_t off = 4;
+    for (int l = 0; l < cfg->n_layers; ++l) {
+      if (cfg->canon_taps > 1) {
+        M->w[l].tail_off = off;
+        off += (int64_t)(cfg->canon_taps - 1) * cfg->width;
+      }
+      if (is_mlstm(layers[l])) {
+        M->w[l].rec_off = off;
+        off += mlstm_state_floats(layers[l].heads, layers[l].dim, layers[l].vdim);
+      }
+      off = up(off, 4);
+    }
+    M->slot_floats = off;
+  }
   b200_model_cfg& mc = c->cfg;
   memset(&mc, 0, sizeof(mc));
   mc.hidden = cfg->width;
@@ -272,6 +523,14 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       shapes.push_back({qkv_rows(layers[l]), (int)Wd});
       shapes.push_back({(int)Wd, layers[l].heads * layers[l].vdim});
       if (layers[l].mlp == B200_MLP_MOE) shapes.push_back({layers[l].experts, (int)Wd});
+      if (layers[l].mlp == B200_MLP_DENSE) {
+        shapes.push_back({2 * layers[l].ff, (int)Wd});
+        shapes.push_back({(int)Wd, layers[l].ff});
+      }
+      if (layers[l].shared_ff > 0) {
+        shapes.push_back({(layers[l].ungated ? 1 : 2) * layers[l].shared_ff, (int)Wd});
+        shapes.push_back({(int)Wd, layers[l].shared_ff});
+      }
     }
     for (auto& sh : shapes) {
       if (sh.second % 8) continue;
@@ -286,7 +545,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     }
   }
   c->lin_ws_bytes = std::max<int64_t>(lw, 64 * 1024);
-  c->meta_ints = 6 * T + T * cfg->max_blocks_per_seq;
+  c->meta_ints = 7 * T + T * cfg->max_blocks_per_seq;
   const int64_t attn_ws_bytes = paged_attn_anydim_workspace_bytes((int)T);
   int tc_heads = 0;
   for (int l = 0; l < cfg->n_layers; ++l)
@@ -324,7 +583,19 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&M->attn_tc_ws, M->attn_tc_ws_bytes},
       {(void**)&M->attn_wide, tc_heads ? T * tc_heads * kHeadDim * 2 : 16},
       {(void**)&c->logits, R * (int64_t)c->logits_ld * 2},
-      {(void**)&c->logits_f32, cfg->f32 ? R * (int64_t)c->logits_ld * 4 : 16},
+      {(void**)&c->logits_f32, (cfg->f32 || par) ? R * (int64_t)c->logits_ld * 4 : 16},
+      {(void**)&M->results, par && cfg->depth_avg ? (int64_t)(cfg->n_layers + 1) * T * Wd * 4 : 16},
+      {(void**)&M->h1f, par && cfg->canon_taps > 1 ? T * Wd * 4 : 16},
+      {(void**)&M->hc, par ? T * Wd * es : 16},
+      {(void**)&M->lat, T * std::max(max_lat, 1) * es},
+      {(void**)&M->y2, par ? T * Wd * es : 16},
+      {(void**)&M->y3, par ? T * Wd * es : 16},
+      {(void**)&M->gu, T * std::max(max_gu, 1) * es},
+      {(void**)&M->ffa, T * std::max(max_ffa, 1) * es},
+      {(void**)&M->gates_buf, T * std::max(max_gates, 1) * 4},
+      {(void**)&M->oraw, max_gates ? T * max_a * 4 : 16},
+      {(void**)&M->head_f32, par ? R * (int64_t)cfg->vocab * 4 : 16},
+      {(void**)&M->seq_start, (T + 2) * 4},
       {(void**)&c->lin_ws, c->lin_ws_bytes},
       {(void**)&c->d_meta, c->meta_ints * 4},
       {(void**)&c->d_tokens, R * 4},
@@ -350,7 +621,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     *it.p = static_cast<char*>(c->pool) + off;
     off += up(std::max<int64_t>(it.bytes, 16), 1024);
   }
-  if (!cfg->f32) c->logits_f32 = nullptr;
+  if (!cfg->f32 && !par) c->logits_f32 = nullptr;
   *out = c;
   return B200_OK;
 }
@@ -360,27 +631,49 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
   B200_REQUIRE(reinterpret_cast<uintptr_t>(w) % 16 == 0, B200_ERR_INVALID, "stack_set_weight: pointer not 16-byte aligned");
   StackModel* M = c->stack;
   const int64_t Wd = M->cfg.width, V = M->cfg.vocab;
-  const bool global = kind == B200_SW_EMBED || kind == B200_SW_FINAL_NORM || kind == B200_SW_HEAD;
+  int64_t er = 0, ec = 1;
+  const bool par = M->cfg.form == B200_FORM_PARALLEL;
+  const bool global = kind == B200_SW_EMBED || kind == B200_SW_FINAL_NORM || kind == B200_SW_HEAD || kind == B200_SW_BIGRAM;
   if (!global) B200_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, B200_ERR_INVALID, "stack_set_weight: layer %d out of range", layer);
   const b200_stack_layer L = global ? b200_stack_layer{} : M->layers[layer];
-  int64_t er = 0, ec = 1;
   switch (kind) {
     case B200_SW_EMBED: case B200_SW_HEAD: er = V; ec = Wd; break;
     case B200_SW_FINAL_NORM: case B200_SW_NORM_MIX_PRE: case B200_SW_NORM_MIX_POST: case B200_SW_NORM_MLP_PRE:
-    case B200_SW_NORM_MLP_POST: er = Wd; break;
+    case B200_SW_NORM_MLP_POST: er = par ? 1 : Wd; break;
     case B200_SW_QKV: er = qkv_rows(L); ec = Wd; break;
     case B200_SW_Q_NORM: er = (int64_t)L.heads * L.dim; break;
-    case B200_SW_K_NORM: er = (int64_t)L.kv_heads * L.dim; break;
+    case B200_SW_K_NORM: er = is_latent(L) ? L.kv_rank : (int64_t)L.kv_heads * L.dim; break;
     case B200_SW_O: er = Wd; ec = (int64_t)L.heads * L.vdim; break;
     case B200_SW_ROUTER: er = L.experts; ec = Wd; break;
     case B200_SW_ROUTER_BIAS: er = L.experts; break;
-    case B200_SW_EXPERT_GATE_UP: er = (int64_t)L.experts * 2 * L.ff; ec = Wd; break;
+    case B200_SW_EXPERT_GATE_UP: er = (int64_t)L.experts * (L.ungated ? 1 : 2) * L.ff; ec = Wd; break;
     case B200_SW_EXPERT_DOWN: er = (int64_t)L.experts * Wd; ec = L.ff; break;
+    case B200_SW_BIGRAM: er = (int64_t)M->cfg.bigram_buckets + 1; ec = Wd; break;
+    case B200_SW_CANON: er = Wd; ec = M->cfg.canon_taps; break;
+    case B200_SW_DEPTH_AVG: er = layer + 2; break;
+    case B200_SW_UK_T: er = (int64_t)L.heads * L.kv_rank; ec = L.dim; break;
+    case B200_SW_UV: er = (int64_t)L.heads * L.vdim; ec = L.kv_rank; break;
+    case B200_SW_SINK: er = L.heads; break;
+    case B200_SW_GATES: er = 2 * (int64_t)L.heads; ec = Wd; break;
+    case B200_SW_GATES_BIAS: er = 2 * (int64_t)L.heads; break;
+    case B200_SW_HEAD_NORM: er = (int64_t)L.heads * L.vdim; break;
+    case B200_SW_MLP_GATE_UP: er = 2 * (int64_t)L.ff; ec = Wd; break;
+    case B200_SW_MLP_DOWN: er = Wd; ec = L.ff; break;
+    case B200_SW_SHARED_UP: er = (int64_t)(L.ungated ? 1 : 2) * L.shared_ff; ec = Wd; break;
+    case B200_SW_SHARED_DOWN: er = Wd; ec = L.shared_ff; break;
     default: B200_REQUIRE(false, B200_ERR_INVALID, "stack_set_weight: unknown kind %d", kind);
   }
+  B200_REQUIRE(kind < B200_SW_BIGRAM || par, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to the parallel form", kind);
+  if (kind == B200_SW_UK_T || kind == B200_SW_UV || kind == B200_SW_SINK)
+    B200_REQUIRE(is_latent(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no latent attention", layer);
+  if (kind == B200_SW_GATES || kind == B200_SW_GATES_BIAS || kind == B200_SW_HEAD_NORM)
+    B200_REQUIRE(is_mlstm(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no recurrence", layer);
+  if (kind == B200_SW_MLP_GATE_UP || kind == B200_SW_MLP_DOWN)
+    B200_REQUIRE(L.mlp == B200_MLP_DENSE, B200_ERR_INVALID, "stack_set_weight: layer %d has no dense feed-forward", layer);
   B200_REQUIRE(rows == er && cols == ec, B200_ERR_INVALID, "stack_set_weight: kind %d of layer %d expects [%lld,%lld], got [%lld,%lld]",
                kind, layer, (long long)er, (long long)ec, (long long)rows, (long long)cols);
-  if (kind >= B200_SW_ROUTER && kind != B200_SW_ROUTER_BIAS)
+  if ((kind >= B200_SW_ROUTER && kind <= B200_SW_EXPERT_DOWN && kind != B200_SW_ROUTER_BIAS) || kind == B200_SW_SHARED_UP ||
+      kind == B200_SW_SHARED_DOWN)
     B200_REQUIRE(L.mlp == B200_MLP_MOE, B200_ERR_INVALID, "stack_set_weight: layer %d has no routed experts", layer);
   const float* f = static_cast<const float*>(w);
   const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(w);
@@ -400,14 +693,28 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_ROUTER_BIAS: M->w[layer].router_bias = f; break;
     case B200_SW_EXPERT_GATE_UP: M->w[layer].e_gate_up = b; break;
     case B200_SW_EXPERT_DOWN: M->w[layer].e_down = b; break;
+    case B200_SW_BIGRAM: M->bigram = b; break;
+    case B200_SW_CANON: M->w[layer].canon = f; break;
+    case B200_SW_DEPTH_AVG: M->w[layer].dwa = f; break;
+    case B200_SW_UK_T: M->w[layer].uk_t = b; break;
+    case B200_SW_UV: M->w[layer].uv = b; break;
+    case B200_SW_SINK: M->w[layer].sink = f; break;
+    case B200_SW_GATES: M->w[layer].gates = b; break;
+    case B200_SW_GATES_BIAS: M->w[layer].gates_bias = f; break;
+    case B200_SW_HEAD_NORM: M->w[layer].head_norm = f; break;
+    case B200_SW_MLP_GATE_UP: M->w[layer].mlp_gate_up = b; break;
+    case B200_SW_MLP_DOWN: M->w[layer].mlp_down = b; break;
+    case B200_SW_SHARED_UP: M->w[layer].shared_up = b; break;
+    case B200_SW_SHARED_DOWN: M->w[layer].shared_down = b; break;
   }
   return B200_OK;
 }
 
 extern "C" int b200_stack_set_kv_cache(b200_ctx* c, int32_t layer, void* k_cache, void* v_cache, int64_t n_blocks) {
-  B200_REQUIRE(c && c->stack && k_cache && v_cache && n_blocks > 0, B200_ERR_INVALID, "stack_set_kv_cache: bad argument");
+  B200_REQUIRE(c && c->stack && k_cache && n_blocks > 0, B200_ERR_INVALID, "stack_set_kv_cache: bad argument");
   StackModel* M = c->stack;
   B200_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, B200_ERR_INVALID, "stack_set_kv_cache: layer %d out of range", layer);
+  B200_REQUIRE(v_cache || cache_vdim(M->cfg, M->layers[layer]) == 0, B200_ERR_INVALID, "stack_set_kv_cache: layer %d needs a value cache", layer);
   B200_REQUIRE(M->n_blocks == 0 || M->n_blocks == n_blocks, B200_ERR_INVALID, "stack_set_kv_cache: every layer needs the same block count");
   M->n_blocks = n_blocks;
   c->n_blocks = n_blocks;
@@ -431,6 +738,22 @@ extern "C" int b200_stack_set_rot_table(b200_ctx* c, int32_t index, const float*
   c->stack->rot[index] = table;
   c->stack->rot_pos[index] = n_pos;
   c->stack->rot_half[index] = half;
+  return B200_OK;
+}
+
+extern "C" int64_t b200_stack_state_bytes(b200_ctx* c) { return c && c->stack ? c->stack->slot_floats * 4 : 0; }
+
+extern "C" int b200_stack_set_state(b200_ctx* c, void* state) {
+  B200_REQUIRE(c && c->stack && state && c->stack->slot_floats > 0, B200_ERR_INVALID, "stack_set_state: not a ctx with state slots");
+  B200_REQUIRE(reinterpret_cast<uintptr_t>(state) % 16 == 0, B200_ERR_INVALID, "stack_set_state: pointer not 16-byte aligned");
+  c->stack->state = static_cast<float*>(state);
+  return B200_OK;
+}
+
+extern "C" int b200_stack_set_step_slots(b200_ctx* c, const int32_t* seq_slots, int32_t n_seqs) {
+  B200_REQUIRE(c && c->stack && n_seqs >= 0, B200_ERR_INVALID, "stack_set_step_slots: bad argument");
+  c->stack->step_slots = seq_slots;
+  c->stack->step_seqs = n_seqs;
   return B200_OK;
 }
 

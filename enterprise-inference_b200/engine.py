@@ -136,7 +136,10 @@ class Scheduler:
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         # numpy mirror of the running sequences' block tables (one row each): the decode fast path
-        # gathers from it instead of walking Python lists
+        # gathers from it instead of walking Python lists.  A sequence's row doubles as its state slot for models that
+        # keep per-sequence state on the device (rows 0 .. max_seqs): a row is handed out with the first blocks of a
+        # sequence and comes back with them (finish, abort, preemption), and a sequence that restarts at position 0
+        # ignores what the slot held.
         self.max_blocks = blocks.blocks_needed(max_model_len) + 1
         self.bt_np = np.zeros((self.max_seqs + 1, self.max_blocks), dtype=np.int32)
         self.free_rows: List[int] = list(range(self.max_seqs, -1, -1))
@@ -291,7 +294,8 @@ class Scheduler:
             ar = np.arange(n, dtype=np.int32)
             stride = int(pos.max()) // bs + 1
             return StepBatch(ids=ids, positions=pos, slots=self.bt_np[rows, pos // bs] * bs + pos % bs,
-                             ctx_lens=pos + 1, row_to_seq=ar, logit_rows=ar, block_tables=self.bt_np[rows, :stride])
+                             ctx_lens=pos + 1, row_to_seq=ar, logit_rows=ar, block_tables=self.bt_np[rows, :stride],
+                             seq_slots=rows.astype(np.int32))
         b = StepBatch()
         for si, s in enumerate(sched):
             r = s.req
@@ -308,6 +312,7 @@ class Scheduler:
             elif s.samples:
                 b.logit_rows.append(len(b.ids) - 1)
             b.block_tables.append(r.block_table)
+            b.seq_slots.append(r.row)
         return b
 
     def mark_launched(self, sched: List[Scheduled]) -> None:
@@ -373,6 +378,8 @@ class LLMEngine:
                  max_model_len: int = 8192):
         self.runner = runner
         self.blocks = BlockManager(runner.n_blocks, runner.block_size)
+        if getattr(runner, "n_state_slots", 0) > 0:      # one state slot per scheduler row (rows 0 .. max_seqs)
+            max_num_seqs = min(max_num_seqs, runner.n_state_slots - 1)
         self.scheduler = Scheduler(self.blocks, max_num_batched_tokens=min(max_num_batched_tokens, runner.max_tokens),
                                    max_num_seqs=max_num_seqs, max_model_len=min(max_model_len, runner.max_model_len))
         self.requests: Dict[str, Request] = {}

@@ -28,6 +28,8 @@ class StepBatch:
     row_to_seq: List[int] = field(default_factory=list)
     logit_rows: List[int] = field(default_factory=list)
     block_tables: List[Sequence[int]] = field(default_factory=list)
+    # models with per-sequence state (recurrent layers, convolution tails): the state slot of every sequence of the step
+    seq_slots: List[int] = field(default_factory=list)
 
     @property
     def n_tokens(self):
@@ -93,7 +95,7 @@ class ModelRunner:
     def _alloc_host_buffers(self, max_logit_rows: int = 512):
         max_tokens = self.max_tokens
         self._weights: List[torch.Tensor] = []   # keeps the borrowed device tensors alive
-        meta_ints = 6 * max_tokens + max_tokens * self.max_blocks_per_seq
+        meta_ints = 7 * max_tokens + max_tokens * self.max_blocks_per_seq
         # two pinned (metadata, tokens) pairs: step_async alternates them, so the host can pack step n+1 while the
         # copies of step n are still in flight; the synchronous calls use pair 0
         self._h_meta2 = [torch.empty(meta_ints, dtype=torch.int32).pin_memory() for _ in range(2)]
@@ -204,7 +206,13 @@ class ModelRunner:
             bt.fill(0)
             for i, row in enumerate(tables):
                 bt[i, :len(row)] = row
-        return T, R, S, bt_stride, o + S * bt_stride
+        n = o + S * bt_stride
+        if getattr(self, "n_state_slots", 0) > 0:
+            if len(b.seq_slots) != S:
+                raise ValueError(f"step of {S} sequences names {len(b.seq_slots)} state slots")
+            a[n:n + S] = b.seq_slots
+            n += S
+        return T, R, S, bt_stride, n
 
     def step(self, b: StepBatch, sync: bool = True) -> np.ndarray:
         """Host-buffer step (the serving path and bench.py's e2e): pinned H2D, step, D2H."""
@@ -391,7 +399,8 @@ class StackRunner(ModelRunner):
 
     def __init__(self, cfg, device: Optional[torch.device] = None, *, max_tokens: int = 2048, max_model_len: int = 8192,
                  block_size: int = 64, n_blocks: Optional[int] = None, kv_cache_gib: Optional[float] = None,
-                 graphs: bool = True, dtype: str = "bfloat16", max_logit_rows: int = 512, tp_rank: int = 0, tp_world: int = 1):
+                 graphs: bool = True, dtype: str = "bfloat16", max_logit_rows: int = 512, tp_rank: int = 0, tp_world: int = 1,
+                 n_state_slots: int = 257):
         if not torch.cuda.is_available():
             raise RuntimeError("StackRunner needs a CUDA device (B200, sm_100a); there is no CPU path")
         if tp_world != 1:
@@ -426,17 +435,41 @@ class StackRunner(ModelRunner):
                 self._tables.append(spec.table(max(max_model_len, 16)).to(self.device))
             return keys[k]
 
+        from .config import DupolornConfig, MLSTMSpec
+        self.parallel = isinstance(cfg, DupolornConfig)
+        self.n_state_slots = int(n_state_slots) if self.parallel and cfg.needs_state else 0
+        if self.parallel and cfg.needs_state and self.n_state_slots <= 0:
+            raise ValueError("this model keeps per-sequence state: n_state_slots must be positive")
         layers = (_abi.StackLayer * cfg.n_layers)()
         for i, L in enumerate(cfg.layers):
             a, f = L.mixer, L.mlp
-            layers[i] = _abi.StackLayer(
-                mixer=_abi.MIXER_ATTENTION, heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim,
-                rot_dims=a.rot.dims if a.rot else 0, rot_table=table_of(a.rot), vrot_table=table_of(a.value_rot), scale=a.scale,
-                mlp=_abi.MLP_MOE if f else _abi.MLP_NONE, experts=f.experts if f else 0, top=f.top if f else 0,
-                groups=f.groups if f else 0, keep=f.keep if f else 0, ff=f.ff if f else 0)
+            if not self.parallel:
+                layers[i] = _abi.StackLayer(
+                    mixer=_abi.MIXER_ATTENTION, heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim,
+                    rot_dims=a.rot.dims if a.rot else 0, rot_table=table_of(a.rot), vrot_table=table_of(a.value_rot), scale=a.scale,
+                    mlp=_abi.MLP_MOE if f else _abi.MLP_NONE, experts=f.experts if f else 0, top=f.top if f else 0,
+                    groups=f.groups if f else 0, keep=f.keep if f else 0, ff=f.ff if f else 0)
+                continue
+            if isinstance(a, MLSTMSpec):
+                d = dict(mixer=_abi.MIXER_MLSTM, heads=a.heads, kv_heads=a.heads, dim=a.dim, vdim=a.vdim, rot_table=-1, vrot_table=-1,
+                         gate_cap=a.gate_cap)
+            else:
+                d = dict(mixer=_abi.MIXER_LATENT, heads=a.heads, kv_heads=1, dim=a.dim, vdim=a.vdim, rot_dims=a.rot.dims if a.rot else 0,
+                         rot_table=table_of(a.rot), vrot_table=-1, scale=a.scale, kv_rank=a.kv_rank, rot_dim=a.rot_dim,
+                         mixer_flags=(_abi.MIXF_SINK if a.sink else 0) | (_abi.MIXF_GATE if a.gate else 0))
+            if f is not None and f.kind == "dense":
+                d.update(mlp=_abi.MLP_DENSE, ff=f.ff, act=_abi.ACTS[f.act])
+            elif f is not None:
+                d.update(mlp=_abi.MLP_MOE, experts=f.experts, top=f.top, groups=1, keep=1, ff=f.ff, act=_abi.ACTS[f.act], ungated=1,
+                         sigmoid_scores=1, weight_input=1, shared_ff=f.shared_ff)
+            layers[i] = _abi.StackLayer(**d)
         sc = _abi.StackCfg(width=cfg.width, vocab=cfg.vocab, n_layers=cfg.n_layers, embed_scale=cfg.embed_scale,
                            norm_eps=cfg.norm_eps, f32=int(self.f32), block_size=block_size, max_tokens=max_tokens,
                            max_blocks_per_seq=self.max_blocks_per_seq, max_logit_rows=min(max_logit_rows, max_tokens))
+        if self.parallel:
+            sc.form, sc.canon_taps, sc.depth_avg = _abi.FORM_PARALLEL, cfg.canon_taps, int(cfg.depth_avg)
+            sc.bigram_buckets, sc.bigram_mul_prev, sc.bigram_mul_cur = cfg.bigram_buckets, cfg.bigram_mul_prev, cfg.bigram_mul_cur
+            sc.logit_softcap, sc.n_state_slots = cfg.logit_softcap, self.n_state_slots
         h = C.c_void_p()
         _abi.check(self.lib.b200_stack_create(C.byref(sc), layers, C.byref(h)))
         self.ctx = h
@@ -450,7 +483,8 @@ class StackRunner(ModelRunner):
             kd, vd = C.c_int32(), C.c_int32()
             _abi.check(self.lib.b200_stack_cache_dims(self.ctx, i, C.byref(kd), C.byref(vd)))
             self.cache_dims.append((kd.value, vd.value))
-        per_block = sum(L.mixer.kv_heads * (kd + vd) for L, (kd, vd) in zip(cfg.layers, self.cache_dims)) * (4 if self.f32 else 2) * block_size
+        kvh = [getattr(L.mixer, "kv_heads", 1) for L in cfg.layers]
+        per_block = max(sum(h * (kd + vd) for h, (kd, vd) in zip(kvh, self.cache_dims)) * (4 if self.f32 else 2) * block_size, 1)
         if n_blocks is None:
             if kv_cache_gib is None:
                 free, _ = torch.cuda.mem_get_info(self.device)
@@ -460,12 +494,20 @@ class StackRunner(ModelRunner):
         cdt = torch.float32 if self.f32 else torch.bfloat16
         self.k_cache, self.v_cache = [], []
         for i, L in enumerate(cfg.layers):
-            a = L.mixer
-            k = torch.zeros((n_blocks, a.kv_heads, block_size, self.cache_dims[i][0]), dtype=cdt, device=self.device)
-            v = torch.zeros((n_blocks, a.kv_heads, block_size, self.cache_dims[i][1]), dtype=cdt, device=self.device)
+            kd, vd = self.cache_dims[i]
+            k = torch.zeros((n_blocks, kvh[i], block_size, kd), dtype=cdt, device=self.device) if kd else None
+            v = torch.zeros((n_blocks, kvh[i], block_size, vd), dtype=cdt, device=self.device) if vd else None
             self.k_cache.append(k)
             self.v_cache.append(v)
-            _abi.check(self.lib.b200_stack_set_kv_cache(self.ctx, i, k.data_ptr(), v.data_ptr(), n_blocks))
+            if k is not None:
+                _abi.check(self.lib.b200_stack_set_kv_cache(self.ctx, i, k.data_ptr(), _abi.ptr(v), n_blocks))
+        # per-sequence state slots (previous token, convolution tails, recurrent state): the scheduler hands a slot to every
+        # running sequence; a sequence that starts at position 0 ignores what the slot held
+        self.state = None
+        if self.n_state_slots > 0:
+            self.state_bytes = int(self.lib.b200_stack_state_bytes(self.ctx))
+            self.state = torch.zeros(self.n_state_slots * self.state_bytes, dtype=torch.uint8, device=self.device)
+            _abi.check(self.lib.b200_stack_set_state(self.ctx, self.state.data_ptr()))
         self._alloc_host_buffers(max_logit_rows)
         self._tap = None
 
@@ -481,8 +523,69 @@ class StackRunner(ModelRunner):
         for layer, kind, t in STACK_WEIGHT_MAPS[self.cfg.architecture](w, self.cfg):
             self._set(layer, kind, t)
 
+    def _init_random_parallel(self, seed: int, std: float):
+        from .config import MLSTMSpec
+        c, A = self.cfg, _abi
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+
+        def rnd(*shape, sd=std):
+            t = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+            t.normal_(0.0, sd, generator=g)
+            return t
+
+        one = torch.ones(1, device=self.device)
+        self._set(0, A.SW_EMBED, rnd(c.vocab, c.width, sd=1.0))
+        if c.bigram_buckets > 0:
+            self._set(0, A.SW_BIGRAM, rnd(c.bigram_buckets + 1, c.width, sd=1.0))
+        self._set(0, A.SW_FINAL_NORM, one)
+        self._set(0, A.SW_HEAD, rnd(c.vocab, c.width))
+        for i, L in enumerate(c.layers):
+            a, f = L.mixer, L.mlp
+            self._set(i, A.SW_NORM_MIX_PRE, one)
+            if f is not None:
+                self._set(i, A.SW_NORM_MLP_PRE, one)
+            if c.canon_taps > 1:
+                self._set(i, A.SW_CANON, rnd(c.width, c.canon_taps, sd=0.2).float())
+            if c.depth_avg:
+                d = torch.full((i + 2,), 0.1 / (i + 1), device=self.device)
+                d[-1] = 0.9
+                self._set(i, A.SW_DEPTH_AVG, d)
+            if isinstance(a, MLSTMSpec):
+                self._set(i, A.SW_QKV, rnd(2 * a.heads * a.dim + 2 * a.heads * a.vdim, c.width))
+                self._set(i, A.SW_GATES, rnd(2 * a.heads, c.width))
+                self._set(i, A.SW_GATES_BIAS, torch.cat([torch.zeros(a.heads), torch.full((a.heads,), 3.0)]).to(self.device))
+                self._set(i, A.SW_HEAD_NORM, torch.ones(a.heads * a.vdim, device=self.device))
+            else:
+                self._set(i, A.SW_QKV, rnd(a.heads * (a.dim + a.rot_dim) + a.kv_rank + a.rot_dim + (a.heads * a.vdim if a.gate else 0), c.width))
+                self._set(i, A.SW_K_NORM, torch.ones(a.kv_rank, device=self.device))
+                self._set(i, A.SW_UK_T, rnd(a.heads * a.kv_rank, a.dim, sd=a.kv_rank ** -0.5))
+                self._set(i, A.SW_UV, rnd(a.heads * a.vdim, a.kv_rank, sd=a.kv_rank ** -0.5))
+                if a.sink:
+                    self._set(i, A.SW_SINK, torch.zeros(a.heads, device=self.device))
+            self._set(i, A.SW_O, rnd(c.width, a.heads * a.vdim))
+            if f is None:
+                continue
+            if f.kind == "dense":
+                self._set(i, A.SW_MLP_GATE_UP, rnd(2 * f.ff, c.width))
+                self._set(i, A.SW_MLP_DOWN, rnd(c.width, f.ff))
+            else:
+                self._set(i, A.SW_ROUTER, rnd(f.experts, c.width))
+                self._set(i, A.SW_EXPERT_GATE_UP, rnd(f.experts * f.ff, c.width))
+                self._set(i, A.SW_EXPERT_DOWN, rnd(f.experts * c.width, f.ff))
+                if f.shared_ff > 0:
+                    self._set(i, A.SW_SHARED_UP, rnd(f.shared_ff, c.width))
+                    self._set(i, A.SW_SHARED_DOWN, rnd(c.width, f.shared_ff))
+
+    def set_step_slots(self, seq_slots: Optional[torch.Tensor]):
+        """Device-pointer steps (step_device) of a model with state slots: int32 device tensor, one slot per sequence of the step."""
+        self._step_slots = seq_slots
+        _abi.check(self.lib.b200_stack_set_step_slots(self.ctx, _abi.ptr(seq_slots), 0 if seq_slots is None else seq_slots.numel()))
+
     def init_random_weights(self, seed: int = 1234, std: float = 0.02):
         """Random-init weights generated on the device (benchmarks).  Norm weights are 1, the router bias 0."""
+        if self.parallel:
+            return self._init_random_parallel(seed, std)
         c, A = self.cfg, _abi
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)
@@ -531,5 +634,5 @@ def make_runner(cfg, **kw):
     if is_stack_config(cfg):
         kw.pop("tp_rank", None), kw.pop("tp_world", None)
         return StackRunner(cfg, **kw)
-    kw.pop("dtype", None), kw.pop("max_logit_rows", None)
+    kw.pop("dtype", None), kw.pop("max_logit_rows", None), kw.pop("n_state_slots", None)
     return ModelRunner(cfg, **kw)

@@ -752,7 +752,8 @@ class _RunnerFactory:
         runner = make_runner(cfg, max_tokens=a.max_num_batched_tokens, max_model_len=a.max_model_len,
                              block_size=a.block_size, kv_cache_gib=a.kv_cache_gib, n_blocks=getattr(a, "n_blocks", None),
                              tp_rank=rank, tp_world=world, graphs=True,
-                             dtype="float32" if a.dtype in ("float32", "fp32", "float") else "bfloat16")
+                             dtype="float32" if a.dtype in ("float32", "fp32", "float") else "bfloat16",
+                             n_state_slots=int(getattr(a, "max_num_seqs", 256)) + 1)
         if a.random_weights or path is None:
             runner.init_random_weights()
         else:

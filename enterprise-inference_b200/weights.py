@@ -119,4 +119,53 @@ def bopilorn_weights(w: Dict[str, torch.Tensor], cfg) -> Iterator[Tuple[int, int
         yield i, A.SW_EXPERT_DOWN, torch.cat([w[f"{p}mlp.e{e}.down"] for e in range(E)], 0)
 
 
-STACK_WEIGHT_MAPS = {"Bopilorn": bopilorn_weights}
+def dupolorn_weights(w: Dict[str, torch.Tensor], cfg) -> Iterator[Tuple[int, int, torch.Tensor]]:
+    """(layer, b200_stack_weight kind, tensor) of a Dupolorn checkpoint: `embed`, `bigram`, `head`, `final.norm`, and per layer i
+    `l<i>.norm1|norm2` (one number each), `l<i>.canon1` [width, taps], `l<i>.dwa` [i + 2], the mixer `l<i>.mix.*` and the
+    feed-forward `l<i>.mlp.*`.  The projections that read the mixer's input are fused row-wise (latent: q | dkv | g; mLSTM:
+    q | k | v | g, and i | f as the gate rows); a head's key expansion is handed over transposed ([heads][kv_rank][dim]); experts are
+    stacked [E][ff][width] and [E][width][ff]; vectors and scalars go over in fp32."""
+    from . import _abi as A
+    from .config import MLSTMSpec
+    yield 0, A.SW_EMBED, w["embed"]
+    if cfg.bigram_buckets > 0:
+        yield 0, A.SW_BIGRAM, w["bigram"]
+    yield 0, A.SW_FINAL_NORM, w["final.norm"].reshape(1)
+    yield 0, A.SW_HEAD, w["head"]
+    for i, L in enumerate(cfg.layers):
+        p, a, f = f"l{i}.", L.mixer, L.mlp
+        yield i, A.SW_NORM_MIX_PRE, w[p + "norm1"].reshape(1)
+        if f is not None:
+            yield i, A.SW_NORM_MLP_PRE, w[p + "norm2"].reshape(1)
+        if cfg.canon_taps > 1:
+            yield i, A.SW_CANON, w[p + "canon1"]
+        if cfg.depth_avg:
+            yield i, A.SW_DEPTH_AVG, w[p + "dwa"]
+        if isinstance(a, MLSTMSpec):
+            yield i, A.SW_QKV, torch.cat([w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"], w[p + "mix.g"]], 0)
+            yield i, A.SW_GATES, torch.cat([w[p + "mix.i"], w[p + "mix.f"]], 0)
+            yield i, A.SW_GATES_BIAS, torch.cat([w[p + "mix.i.b"], w[p + "mix.f.b"]], 0)
+            yield i, A.SW_HEAD_NORM, w[p + "mix.norm"]
+        else:
+            yield i, A.SW_QKV, torch.cat([w[p + "mix.q"], w[p + "mix.dkv"]] + ([w[p + "mix.g"]] if a.gate else []), 0)
+            yield i, A.SW_K_NORM, w[p + "mix.dkv.norm"]
+            yield i, A.SW_UK_T, w[p + "mix.uk"].reshape(a.heads, a.dim, a.kv_rank).transpose(1, 2).reshape(a.heads * a.kv_rank, a.dim)
+            yield i, A.SW_UV, w[p + "mix.uv"]
+            if a.sink:
+                yield i, A.SW_SINK, w[p + "mix.sink"]
+        yield i, A.SW_O, w[p + "mix.o"]
+        if f is None:
+            continue
+        if f.kind == "dense":
+            yield i, A.SW_MLP_GATE_UP, torch.cat([w[p + "mlp.gate"], w[p + "mlp.up"]], 0)
+            yield i, A.SW_MLP_DOWN, w[p + "mlp.down"]
+        else:
+            yield i, A.SW_ROUTER, w[p + "mlp.router"]
+            yield i, A.SW_EXPERT_GATE_UP, torch.cat([w[f"{p}mlp.e{e}.up"] for e in range(f.experts)], 0)
+            yield i, A.SW_EXPERT_DOWN, torch.cat([w[f"{p}mlp.e{e}.down"] for e in range(f.experts)], 0)
+            if f.shared_ff > 0:
+                yield i, A.SW_SHARED_UP, w[p + "mlp.shared.up"]
+                yield i, A.SW_SHARED_DOWN, w[p + "mlp.shared.down"]
+
+
+STACK_WEIGHT_MAPS = {"Bopilorn": bopilorn_weights, "Dupolorn": dupolorn_weights}

@@ -135,7 +135,8 @@ B200_API int b200_decode_step(b200_ctx* ctx, const int32_t* ids, const int32_t* 
 
 /* Same step, driven from PINNED HOST memory: one packed int32 buffer
  *   [ids | positions | slot_mapping | ctx_lens | row_to_seq | logit_rows](each n_tokens, the
- *   last n_logit_rows) followed by block_table [n_seqs][bt_stride],
+ *   last n_logit_rows) followed by block_table [n_seqs][bt_stride] (and, for a ctx with per-sequence state slots,
+ *   seq_slots [n_seqs]: see b200_stack_set_state),
  * copied H2D, the step, and the sampled ids copied D2H into host_out_token_ids.  The copies
  * are enqueued on `stream`; the caller synchronises.  This is the call the serving engine
  * makes every iteration (the `e2e` figure of bench.py).
@@ -367,9 +368,34 @@ B200_API int b200_tp_allreduce(b200_ctx* ctx, int32_t buf_idx, const void* parti
  *
  * B200_MLP_MOE: routed experts.  Router softmax over all experts; choice by score + bias, group-limited (experts in
  * `groups` equal runs of neighbours, only the `keep` best groups eligible), `top` experts; mixing weights = the plain
- * softmax scores, not renormalised; expert = down(silu(gate x) * (up x)). */
-typedef enum b200_mixer_kind { B200_MIXER_ATTENTION = 1 } b200_mixer_kind;
-typedef enum b200_mlp_kind { B200_MLP_NONE = 0, B200_MLP_MOE = 1 } b200_mlp_kind;
+ * softmax scores, not renormalised; expert = down(silu(gate x) * (up x)).
+ *
+ * Second layer form (b200_stack_cfg.form = B200_FORM_PARALLEL): both sublayers read the same stream,
+ *   x_next = x + mixer(h1 + conv(h1)) + ff(h2),   h1 = x / rms(x) * g1,  h2 = x / rms(x) * g2   (g1, g2: one number each),
+ * conv a causal per-channel convolution over `canon_taps` time steps (0: none), and, with depth_avg, the stream handed to
+ * the next layer is a weighted sum of the embedding output and of every layer result so far.  Models of this form may
+ * add a hashed bigram table to the embedding, cap the logits with cap * tanh(z / cap), and use
+ *
+ * B200_MIXER_LATENT: causal softmax attention whose keys and values are expanded from ONE cached vector per token.  The
+ * fused projection gives, per token, the queries (per head `dim` plain and `rot_dim` rotated dimensions), a latent of
+ * `kv_rank` dimensions (RMS-normalised with a weight) and one rotated key part of `rot_dim` dimensions shared by all heads;
+ * a head's plain key is W_uk c and its value W_uv c.  The cache row is [c | rotated key part]; scores are taken in the
+ * latent space (q' = W_uk^T q, one kv head of kv_rank + rot_dim dimensions whose value is the row's first kv_rank entries),
+ * the weighted latent sum is expanded by W_uv.  mixer_flags: B200_MIXF_SINK adds exp(sink[head]) to the softmax
+ * denominator; B200_MIXF_GATE multiplies the concatenated heads by sigmoid(W_g h).
+ *
+ * B200_MIXER_MLSTM: matrix-memory recurrence per head, fp32 state S [dim][vdim], n [dim], m carried per sequence in a state
+ * slot: log gates i = cap tanh((W_i h + b_i) / cap), f = logsigmoid(cap tanh((W_f h + b_f) / cap));
+ * m' = max(f + m, i); S' = exp(f + m - m') S + exp(i - m') k v^T (n' likewise with k); o = S'^T q / (max(|n'.q|, exp(-m')) + 1e-6)
+ * with q scaled by dim^-1/2; each head's o is brought to unit RMS, times a weight, times sigmoid(W_g h).
+ *
+ * B200_MLP_DENSE: down(act(gate x) * (up x)).  Routed experts of this form may score with a sigmoid, apply the mixing
+ * weight to the expert's INPUT, be ungated (down(act(up x))), and come with one shared expert of the same shape. */
+typedef enum b200_mixer_kind { B200_MIXER_ATTENTION = 1, B200_MIXER_LATENT = 2, B200_MIXER_MLSTM = 3 } b200_mixer_kind;
+typedef enum b200_mlp_kind { B200_MLP_NONE = 0, B200_MLP_MOE = 1, B200_MLP_DENSE = 2 } b200_mlp_kind;
+typedef enum b200_act_kind { B200_ACT_SILU = 0, B200_ACT_GELU_TANH = 1, B200_ACT_RELU2 = 2 } b200_act_kind;
+typedef enum b200_stack_form { B200_FORM_SANDWICH = 0, B200_FORM_PARALLEL = 1 } b200_stack_form;
+enum { B200_MIXF_SINK = 1, B200_MIXF_GATE = 2 };
 
 typedef struct b200_stack_layer {
   int32_t mixer;                       /* b200_mixer_kind */
@@ -379,6 +405,16 @@ typedef struct b200_stack_layer {
   float scale;                         /* score scale */
   int32_t mlp;                         /* b200_mlp_kind */
   int32_t experts, top, groups, keep, ff;
+  /* everything below: 0 = the first form's behaviour */
+  int32_t kv_rank, rot_dim;            /* latent mixer: latent size; rotated part of a query head and of the shared key
+                                          (rot_dims <= rot_dim of them turn) */
+  int32_t mixer_flags;                 /* B200_MIXF_* */
+  float gate_cap;                      /* mLSTM */
+  int32_t act;                         /* b200_act_kind of the feed-forward */
+  int32_t ungated;                     /* experts without a gate projection */
+  int32_t sigmoid_scores;              /* router scores are sigmoids of the logits (no softmax) */
+  int32_t weight_input;                /* the mixing weight multiplies the expert's input instead of its output */
+  int32_t shared_ff;                   /* intermediate size of the shared expert (0: none) */
 } b200_stack_layer;
 
 typedef struct b200_stack_cfg {
@@ -388,24 +424,46 @@ typedef struct b200_stack_cfg {
   int32_t f32;                         /* 0: bf16 activations, cache and matrix products (fp32 accumulation; residual stream,
                                           norms, rotations, scores, softmax and routers in fp32); 1: everything in true fp32 */
   int32_t block_size, max_tokens, max_blocks_per_seq, max_logit_rows;
+  /* everything below: 0 = the first form's behaviour */
+  int32_t form;                        /* b200_stack_form */
+  int32_t canon_taps;                  /* taps of the input convolution of every mixer (0: none) */
+  int32_t depth_avg;                   /* 1: weighted sum over all earlier layer results after every layer */
+  int32_t bigram_buckets, bigram_mul_prev, bigram_mul_cur;   /* buckets > 0: hashed bigram rows are added to the embedding */
+  float logit_softcap;                 /* > 0: logits = cap * tanh(logits / cap) */
+  int32_t n_state_slots;               /* per-sequence state slots (previous token, convolution tails, recurrent state) */
 } b200_stack_cfg;
 
 typedef enum b200_stack_weight {
   B200_SW_EMBED = 0,        /* bf16 [vocab][width] */
-  B200_SW_FINAL_NORM = 1,   /* f32  [width] */
+  B200_SW_FINAL_NORM = 1,   /* f32  [width]   (parallel form: [1]) */
   B200_SW_HEAD = 2,         /* bf16 [vocab][width] */
-  B200_SW_NORM_MIX_PRE = 3, /* f32  [width]  the four layer norms of a layer */
+  B200_SW_NORM_MIX_PRE = 3, /* f32  [width]  the four layer norms of a layer (parallel form: PRE kinds only, [1] each) */
   B200_SW_NORM_MIX_POST = 4,
   B200_SW_NORM_MLP_PRE = 5,
   B200_SW_NORM_MLP_POST = 6,
-  B200_SW_QKV = 7,          /* bf16 [heads*dim + kv_heads*dim + kv_heads*vdim][width]: q rows, k rows, v rows */
+  B200_SW_QKV = 7,          /* bf16, fused projection of the mixer's input.  attention: [heads*dim + kv_heads*dim + kv_heads*vdim][width]
+                               (q, k, v rows); latent: [heads*(dim+rot_dim) + kv_rank + rot_dim (+ heads*vdim gate rows)][width];
+                               mLSTM: [2*heads*dim + 2*heads*vdim][width] (q, k, v, output-gate rows) */
   B200_SW_Q_NORM = 8,       /* f32  [heads*dim] */
-  B200_SW_K_NORM = 9,       /* f32  [kv_heads*dim] */
+  B200_SW_K_NORM = 9,       /* f32  [kv_heads*dim]   (latent: [kv_rank], the latent's norm weight) */
   B200_SW_O = 10,           /* bf16 [width][heads*vdim] */
   B200_SW_ROUTER = 11,      /* bf16 [experts][width] */
   B200_SW_ROUTER_BIAS = 12, /* f32  [experts]  added to the scores for the choice only (may stay unset: zeros) */
-  B200_SW_EXPERT_GATE_UP = 13, /* bf16 [experts][2*ff][width]: per expert the gate rows, then the up rows */
-  B200_SW_EXPERT_DOWN = 14  /* bf16 [experts][width][ff] */
+  B200_SW_EXPERT_GATE_UP = 13, /* bf16 [experts][2*ff][width]: per expert the gate rows, then the up rows (ungated: [experts][ff][width]) */
+  B200_SW_EXPERT_DOWN = 14, /* bf16 [experts][width][ff] */
+  B200_SW_BIGRAM = 15,      /* bf16 [bigram_buckets + 1][width]; the last row serves a sequence's first token */
+  B200_SW_CANON = 16,       /* f32  [width][canon_taps] */
+  B200_SW_DEPTH_AVG = 17,   /* f32  [layer + 2] */
+  B200_SW_UK_T = 18,        /* bf16 [heads][kv_rank][dim]: per head the TRANSPOSE of its key expansion */
+  B200_SW_UV = 19,          /* bf16 [heads][vdim][kv_rank] */
+  B200_SW_SINK = 20,        /* f32  [heads] */
+  B200_SW_GATES = 21,       /* bf16 [2*heads][width]: mLSTM input-gate rows, then forget-gate rows */
+  B200_SW_GATES_BIAS = 22,  /* f32  [2*heads] */
+  B200_SW_HEAD_NORM = 23,   /* f32  [heads*vdim] */
+  B200_SW_MLP_GATE_UP = 24, /* bf16 [2*ff][width]: gate rows, then up rows */
+  B200_SW_MLP_DOWN = 25,    /* bf16 [width][ff] */
+  B200_SW_SHARED_UP = 26,   /* bf16 [shared_ff][width] */
+  B200_SW_SHARED_DOWN = 27  /* bf16 [width][shared_ff] */
 } b200_stack_weight;
 
 B200_API int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_layer* layers, b200_ctx** out);
@@ -422,6 +480,13 @@ B200_API int b200_stack_set_rot_table(b200_ctx* ctx, int32_t index, const float*
 /* After every layer of a step, the residual stream is copied to out[layer][n_tokens][width] fp32 (NULL: off; turns graph
  * replay off while set).  Parity tests. */
 B200_API int b200_stack_set_stream_tap(b200_ctx* ctx, float* out);
+/* Per-sequence state (models with n_state_slots > 0): caller-owned, n_state_slots * b200_stack_state_bytes(ctx) bytes, any
+ * content (a sequence whose first row of a step is at position 0 starts from zeros).  A step names the slot of each of its
+ * sequences: the host-buffer step reads seq_slots[n_seqs] behind the block tables of its packed buffer; device-pointer
+ * steps use the array given here (device memory, n_seqs entries, read at every following step until replaced). */
+B200_API int64_t b200_stack_state_bytes(b200_ctx* ctx);
+B200_API int b200_stack_set_state(b200_ctx* ctx, void* state);
+B200_API int b200_stack_set_step_slots(b200_ctx* ctx, const int32_t* seq_slots, int32_t n_seqs);
 /* The logit rows of the LAST step as fp32 [n_rows][vocab] into host memory (asynchronously: synchronise the stream before
  * reading).  With f32 they are the unrounded logits; otherwise the bf16 logits widened.  Works for every ctx on one GPU. */
 B200_API int b200_ctx_logits_last_f32(b200_ctx* ctx, int32_t n_rows, float* host_out, void* stream);
