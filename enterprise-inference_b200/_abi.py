@@ -131,6 +131,22 @@ SIGNATURES = {
     "b200_moe_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32, _i32]),
     "b200_moe_experts": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "b200_linear_simt": (C.c_int, [_i32, _i32, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
+    "b200_seq_bounds": (C.c_int, [_vp, _i32, _i32, _vp, _vp]),
+    "b200_embed_bigram": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _i32, _i32, _i32, _vp]),
+    "b200_parallel_close": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
+                                      _f32, _vp]),
+    "b200_canon_conv": (C.c_int, [_i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "b200_latent_prep": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "b200_head_linear": (C.c_int, [_i32, _i32, _vp, _i64, _i32, _vp, _vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200_paged_attn_anydim_ex": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f32,
+                                            _i32, _vp, _i32, _i32, _vp, _vp]),
+    "b200_mlstm_gates": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
+    "b200_mlstm_state_floats": (_i64, [_i32, _i32, _i32]),
+    "b200_mlstm_scan": (C.c_int, [_i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "b200_head_norm_gate": (C.c_int, [_i32, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _f32, _vp]),
+    "b200_ff_act": (C.c_int, [_i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "b200_moe_route_scores": (C.c_int, [_i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "b200_moe_experts_form": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
 }
 
 _lib = None

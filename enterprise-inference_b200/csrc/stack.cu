@@ -215,7 +215,7 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
                     seq_slots, stateful ? st_prev : nullptr, M->slot_floats, m.bigram_buckets, m.bigram_mul_prev, m.bigram_mul_cur, s));
   if (stateful && m.bigram_buckets > 0)
     STEP(prev_token_commit(a.ids, m.vocab, a.prev_tokens, a.n_prev, M->seq_start, seq_slots, S, st_prev, M->slot_floats, s));
-  const bool conv = m.canon_taps > 1;
+  const bool conv = m.canon_taps >= 1;
   // X_0 and the first layer's norms
   STEP(parallel_close(f32, u, nullptr, nullptr, nullptr, 0, nullptr, m.depth_avg ? M->results : nullptr, rstride, 1, nullptr,
                       M->w[0].n_mix_pre, M->w[0].n_mlp_pre, conv ? M->h1f : nullptr, conv ? nullptr : M->hc, M->hn, T, Wd, m.norm_eps, s));
@@ -225,7 +225,7 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
     const int qr = qkv_rows(L);
     if (conv)
       STEP(canon_conv(f32, M->h1f, W.canon, M->hc, T, Wd, m.canon_taps, a.positions, a.row_to_seq, M->seq_start, seq_slots,
-                      M->state + W.tail_off, M->slot_floats, s));
+                      M->state ? M->state + W.tail_off : nullptr, M->slot_floats, s));
     STEP(stack_linear(c, M->hc, Wd, W.qkv, M->qkv, qr, T, qr, Wd, s));
     const int av = L.heads * L.vdim;
     if (is_latent(L)) {
@@ -464,8 +464,8 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
   const bool par = cfg->form == B200_FORM_PARALLEL;
   B200_REQUIRE(par || (!cfg->canon_taps && !cfg->depth_avg && !cfg->bigram_buckets && cfg->logit_softcap == 0.f), B200_ERR_UNSUPPORTED,
                "stack_create: convolution, depth average, bigram rows and the logit cap belong to the parallel form");
-  B200_REQUIRE(!par || ((cfg->canon_taps == 0 || (cfg->canon_taps >= 2 && cfg->canon_taps <= 8)) && cfg->n_state_slots >= 0 &&
-                        ((cfg->canon_taps == 0 && cfg->bigram_buckets <= 0) || cfg->n_state_slots > 0)),
+  B200_REQUIRE(!par || (cfg->canon_taps >= 0 && cfg->canon_taps <= 8 && cfg->n_state_slots >= 0 &&
+                        ((cfg->canon_taps <= 1 && cfg->bigram_buckets <= 0) || cfg->n_state_slots > 0)),
                B200_ERR_INVALID, "stack_create: bad convolution taps or no state slots");
   b200_ctx* c = new b200_ctx();
   StackModel* M = new StackModel();
@@ -585,7 +585,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&c->logits, R * (int64_t)c->logits_ld * 2},
       {(void**)&c->logits_f32, (cfg->f32 || par) ? R * (int64_t)c->logits_ld * 4 : 16},
       {(void**)&M->results, par && cfg->depth_avg ? (int64_t)(cfg->n_layers + 1) * T * Wd * 4 : 16},
-      {(void**)&M->h1f, par && cfg->canon_taps > 1 ? T * Wd * 4 : 16},
+      {(void**)&M->h1f, par && cfg->canon_taps >= 1 ? T * Wd * 4 : 16},
       {(void**)&M->hc, par ? T * Wd * es : 16},
       {(void**)&M->lat, T * std::max(max_lat, 1) * es},
       {(void**)&M->y2, par ? T * Wd * es : 16},
@@ -871,4 +871,115 @@ extern "C" int b200_linear_simt(int32_t x_f32, int32_t y_f32, const void* x, int
                                 int32_t T, int32_t n_out, int32_t k, void* stream) {
   B200_REQUIRE(x && w && y && T >= 0 && n_out > 0 && k > 0, B200_ERR_INVALID, "linear_simt: bad argument");
   return linear_simt(x_f32 != 0, y_f32 != 0, x, ldx, (const __nv_bfloat16*)w, y, ldy, T, n_out, k, (cudaStream_t)stream);
+}
+
+// ---- per-kernel entry points of the parallel form ---------------------------------------------------------------------------
+extern "C" int b200_seq_bounds(const int32_t* row_to_seq, int32_t T, int32_t n_seqs, int32_t* seq_start, void* stream) {
+  B200_REQUIRE(seq_start && T >= 0 && n_seqs >= 0, B200_ERR_INVALID, "seq_bounds: bad argument");
+  return seq_bounds(row_to_seq, T, n_seqs, seq_start, (cudaStream_t)stream);
+}
+
+extern "C" int b200_embed_bigram(const int32_t* ids, const void* table, const void* bigram, float* out, int32_t T, int32_t width,
+                                 int32_t vocab, float scale, const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start,
+                                 const int32_t* seq_slots, int32_t n_seqs, int32_t* state_prev, int64_t slot_stride_ints, int32_t buckets,
+                                 int32_t mul_prev, int32_t mul_cur, void* stream) {
+  B200_REQUIRE(ids && table && out && width > 0 && vocab > 0, B200_ERR_INVALID, "embed_bigram: bad argument");
+  int rc = embed_bigram(ids, (const __nv_bfloat16*)table, (const __nv_bfloat16*)bigram, out, T, width, vocab, scale, nullptr, 0, positions,
+                        row_to_seq, seq_slots, state_prev, slot_stride_ints, buckets, mul_prev, mul_cur, (cudaStream_t)stream);
+  if (rc || !state_prev) return rc;
+  B200_REQUIRE(seq_start && seq_slots, B200_ERR_INVALID, "embed_bigram: sequence bounds / slots missing");
+  return prev_token_commit(ids, vocab, nullptr, 0, seq_start, seq_slots, n_seqs, state_prev, slot_stride_ints, (cudaStream_t)stream);
+}
+
+extern "C" int b200_parallel_close(int32_t f32, float* u, const void* y_mix, const void* y_ff, const float* parts, int32_t n_parts,
+                                   const void* y_sh, float* results, int64_t result_stride, int32_t n_results, const float* dwa,
+                                   const float* g1, const float* g2, float* h1_f32, void* h1_act, void* h2, int32_t T, int32_t width,
+                                   float eps, void* stream) {
+  B200_REQUIRE(u && T >= 0 && width > 0 && n_results >= 1, B200_ERR_INVALID, "parallel_close: bad argument");
+  return parallel_close(f32 != 0, u, y_mix, y_ff, parts, n_parts, y_sh, results, result_stride, n_results, dwa, g1, g2, h1_f32, h1_act, h2,
+                        T, width, eps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_canon_conv(int32_t f32, const float* h, const float* w, void* out, int32_t T, int32_t width, int32_t taps,
+                               const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots,
+                               float* tails, int64_t slot_stride, void* stream) {
+  B200_REQUIRE(h && w && out && width > 0, B200_ERR_INVALID, "canon_conv: bad argument");
+  return canon_conv(f32 != 0, h, w, out, T, width, taps, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride,
+                    (cudaStream_t)stream);
+}
+
+extern "C" int b200_latent_prep(int32_t f32, const void* qkv, int64_t ld, const float* norm_w, const int32_t* positions,
+                                const int32_t* slots, const float* rot, int32_t rot_dims, int64_t max_pos, float* qfull, void* cache,
+                                int32_t T, int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float eps, void* stream) {
+  B200_REQUIRE(qkv && norm_w && positions && slots && qfull && cache && heads > 0 && kv_rank > 0 && max_pos > 0, B200_ERR_INVALID,
+               "latent_prep: bad argument");
+  return latent_prep(f32 != 0, qkv, ld, norm_w, positions, slots, rot, rot_dims, max_pos, qfull, cache, T, heads, dim, rot_dim, kv_rank, eps,
+                     (cudaStream_t)stream);
+}
+
+extern "C" int b200_head_linear(int32_t f32, int32_t y_f32, const void* x, int64_t ldx, int32_t x_hs, const void* w, void* y, int64_t ldy,
+                                int32_t y_hs, const void* gate, int64_t ldg, int32_t g_hs, int32_t T, int32_t heads, int32_t n_out, int32_t k,
+                                void* stream) {
+  B200_REQUIRE(x && w && y && heads > 0 && n_out > 0 && k > 0, B200_ERR_INVALID, "head_linear: bad argument");
+  return head_linear(f32 != 0, y_f32 != 0, x, ldx, x_hs, (const __nv_bfloat16*)w, y, ldy, y_hs, gate, ldg, g_hs, T, heads, n_out, k,
+                     (cudaStream_t)stream);
+}
+
+extern "C" int b200_paged_attn_anydim_ex(int32_t f32, const float* q, const void* kc, const void* vc, const int32_t* block_table,
+                                         int32_t bt_stride, const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions,
+                                         void* out, int32_t T, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t block_size,
+                                         float scale, int32_t shared_tiles, void* ws, int32_t k_row, int32_t v_row, const float* sink,
+                                         void* stream) {
+  B200_REQUIRE(q && kc && vc && block_table && ctx_lens && positions && out && block_size > 0, B200_ERR_INVALID,
+               "paged_attn_anydim_ex: bad argument");
+  B200_REQUIRE(!shared_tiles || ws, B200_ERR_INVALID, "paged_attn_anydim_ex: the shared-tile form needs its workspace");
+  return paged_attn_anydim(f32 != 0, q, kc, vc, block_table, bt_stride, row_to_seq, ctx_lens, positions, nullptr, 1ll << 40, out, T, heads,
+                           kv_heads, dim, vdim, block_size, scale, shared_tiles ? 1 : 0, ws, (cudaStream_t)stream, k_row, v_row, sink);
+}
+
+extern "C" int b200_mlstm_gates(int32_t f32, const void* x, const void* w, const float* bias, float* out, int32_t T, int32_t width,
+                                int32_t heads, float cap, void* stream) {
+  B200_REQUIRE(x && w && out && width > 0 && heads > 0, B200_ERR_INVALID, "mlstm_gates: bad argument");
+  return mlstm_gates(f32 != 0, x, (const __nv_bfloat16*)w, bias, out, T, width, heads, cap, (cudaStream_t)stream);
+}
+
+extern "C" int64_t b200_mlstm_state_floats(int32_t heads, int32_t dim, int32_t vdim) { return mlstm_state_floats(heads, dim, vdim); }
+
+extern "C" int b200_mlstm_scan(int32_t f32, const void* qkv, int64_t ld, int32_t q_off, int32_t k_off, int32_t v_off, const float* gates,
+                               const int32_t* positions, const int32_t* seq_start, const int32_t* seq_slots, float* state,
+                               int64_t slot_stride, float* out, int32_t n_seqs, int32_t heads, int32_t dim, int32_t vdim, void* stream) {
+  B200_REQUIRE(qkv && gates && out && heads > 0, B200_ERR_INVALID, "mlstm_scan: bad argument");
+  return mlstm_scan(f32 != 0, qkv, ld, q_off, k_off, v_off, gates, positions, seq_start, seq_slots, state, slot_stride, out, n_seqs, heads,
+                    dim, vdim, (cudaStream_t)stream);
+}
+
+extern "C" int b200_head_norm_gate(int32_t f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int32_t T,
+                                   int32_t heads, int32_t vdim, float eps, void* stream) {
+  B200_REQUIRE(o && out && heads > 0 && vdim > 0, B200_ERR_INVALID, "head_norm_gate: bad argument");
+  return head_norm_gate(f32 != 0, o, w, gate, ldg, out, T, heads, vdim, eps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_ff_act(int32_t f32, const void* in, void* out, int32_t T, int32_t ff, int32_t gated, int32_t act, void* stream) {
+  B200_REQUIRE(in && out && ff > 0 && act >= 0 && act <= B200_ACT_RELU2, B200_ERR_INVALID, "ff_act: bad argument");
+  return ff_act(f32 != 0, in, out, T, ff, gated != 0, act, (cudaStream_t)stream);
+}
+
+extern "C" int b200_moe_route_scores(int32_t f32, const void* x, const void* w_router, int32_t T, int32_t width, int32_t experts,
+                                     int32_t top, int32_t sigmoid_scores, int32_t* out_ids, float* out_w, void* stream) {
+  B200_REQUIRE(x && w_router && out_ids && out_w && width > 0, B200_ERR_INVALID, "moe_route_scores: bad argument");
+  return moe_route(f32 != 0, x, (const __nv_bfloat16*)w_router, nullptr, T, width, experts, top, 1, 1, out_ids, out_w, (cudaStream_t)stream,
+                   nullptr, nullptr, 0, sigmoid_scores != 0);
+}
+
+extern "C" int b200_moe_experts_form(int32_t f32, const void* x, const void* w_up, const void* w_down, const int32_t* ids, const float* wts,
+                                     int32_t T, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts, void* ws,
+                                     int32_t gated, int32_t act, int32_t weight_input, void* stream) {
+  B200_REQUIRE(x && w_up && w_down && ids && wts && parts && width > 0 && ff > 0 && experts > 0 && top > 0, B200_ERR_INVALID,
+               "moe_experts_form: bad argument");
+  ExpertForm form;
+  form.gated = gated != 0;
+  form.act = act;
+  form.weight_input = weight_input != 0;
+  return moe_experts(f32 != 0, x, (const __nv_bfloat16*)w_up, (const __nv_bfloat16*)w_down, ids, wts, T, width, ff, experts, top, parts, ws,
+                     (cudaStream_t)stream, form);
 }

@@ -161,7 +161,8 @@ canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* 
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int s = row_to_seq ? row_to_seq[t] : t;
-  const int start = seq_start[s], n = seq_start[s + 1] - start, r = t - start, hist = taps - 1;
+  const int hist = taps - 1;
+  const int start = hist ? seq_start[s] : t, n = hist ? seq_start[s + 1] - start : 1, r = t - start;
   if (r >= hist) {
     for (int c = threadIdx.x; c < width; c += 256) {
       float a = h[(int64_t)t * width + c];
@@ -307,8 +308,8 @@ int canon_conv(bool f32, const float* h, const float* w, void* out, int T, int w
                const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots, float* tails, int64_t slot_stride,
                cudaStream_t s) {
   if (T == 0) return B200_OK;
-  B200_REQUIRE(taps >= 2 && taps <= kMaxTaps, B200_ERR_UNSUPPORTED, "canon_conv: %d taps outside [2, %d]", taps, kMaxTaps);
-  B200_REQUIRE(positions && seq_start && seq_slots && tails, B200_ERR_INVALID, "canon_conv: null argument");
+  B200_REQUIRE(taps >= 1 && taps <= kMaxTaps, B200_ERR_UNSUPPORTED, "canon_conv: %d taps outside [1, %d]", taps, kMaxTaps);
+  B200_REQUIRE(taps == 1 || (positions && seq_start && seq_slots && tails), B200_ERR_INVALID, "canon_conv: null argument");
   if (f32)
     B200_CUDA(launch(canon_conv_kernel<float>, dim3(T), dim3(256), (size_t)0, s, h, w, (float*)out, width, taps, positions, row_to_seq,
                      seq_start, seq_slots, tails, slot_stride));

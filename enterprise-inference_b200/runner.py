@@ -545,7 +545,7 @@ class StackRunner(ModelRunner):
             self._set(i, A.SW_NORM_MIX_PRE, one)
             if f is not None:
                 self._set(i, A.SW_NORM_MLP_PRE, one)
-            if c.canon_taps > 1:
+            if c.canon_taps >= 1:
                 self._set(i, A.SW_CANON, rnd(c.width, c.canon_taps, sd=0.2).float())
             if c.depth_avg:
                 d = torch.full((i + 2,), 0.1 / (i + 1), device=self.device)

@@ -137,7 +137,7 @@ def dupolorn_weights(w: Dict[str, torch.Tensor], cfg) -> Iterator[Tuple[int, int
         yield i, A.SW_NORM_MIX_PRE, w[p + "norm1"].reshape(1)
         if f is not None:
             yield i, A.SW_NORM_MLP_PRE, w[p + "norm2"].reshape(1)
-        if cfg.canon_taps > 1:
+        if cfg.canon_taps >= 1:
             yield i, A.SW_CANON, w[p + "canon1"]
         if cfg.depth_avg:
             yield i, A.SW_DEPTH_AVG, w[p + "dwa"]

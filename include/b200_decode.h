@@ -526,6 +526,66 @@ B200_API int b200_paged_attn_anydim(int32_t f32, const float* q, const void* k_c
                            const float* vrot, int64_t max_pos, void* out, int32_t n_tokens, int32_t heads, int32_t kv_heads,
                            int32_t dim, int32_t vdim, int32_t block_size, float scale, int32_t shared_tiles, void* workspace,
                            void* stream);
+/* ---- per-kernel entry points of the parallel form (unit tests, profiling); f32 as above ---- */
+/* seq_start[s] = first row of sequence s of the step, seq_start[n_seqs] = n_tokens (row_to_seq NULL: every row its own). */
+B200_API int b200_seq_bounds(const int32_t* row_to_seq, int32_t n_tokens, int32_t n_seqs, int32_t* seq_start, void* stream);
+/* out[t] = table[id] * scale + bigram[(prev * mul_prev + id * mul_cur) mod buckets] (row `buckets` at position 0); prev is the
+ * row before in the same sequence or state_prev[slot * slot_stride_ints]; with state_prev the last id of every sequence is
+ * stored there afterwards. */
+B200_API int b200_embed_bigram(const int32_t* ids, const void* table, const void* bigram, float* out, int32_t n_tokens, int32_t width,
+                               int32_t vocab, float scale, const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start,
+                               const int32_t* seq_slots, int32_t n_seqs, int32_t* state_prev, int64_t slot_stride_ints, int32_t buckets,
+                               int32_t mul_prev, int32_t mul_cur, void* stream);
+/* The closing pass of a layer over fp32 rows u [T][width]: with y_mix, X = u + (y_mix + y_ff + sum of n_parts fp32 partial rows +
+ * y_sh) (each optional but y_mix); `results` [n_results][result_stride] receives X (or u) as entry n_results - 1; with dwa,
+ * u = sum_j dwa[j] results[j], else u = X; with g1, h1 = u / rms(u) * g1[0] (fp32 and / or activation type) and h2 likewise. */
+B200_API int b200_parallel_close(int32_t f32, float* u, const void* y_mix, const void* y_ff, const float* parts, int32_t n_parts,
+                                 const void* y_sh, float* results, int64_t result_stride, int32_t n_results, const float* dwa,
+                                 const float* g1, const float* g2, float* h1_f32, void* h1_act, void* h2, int32_t n_tokens, int32_t width,
+                                 float eps, void* stream);
+/* out[t] = h[t] + sum_j w[:, j] h[t - taps + 1 + j] along each sequence; tails [slot][taps - 1][width] (slot_stride floats apart)
+ * hold the inputs before the step's portion and receive its last taps - 1 inputs. */
+B200_API int b200_canon_conv(int32_t f32, const float* h, const float* w, void* out, int32_t n_tokens, int32_t width, int32_t taps,
+                             const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots,
+                             float* tails, int64_t slot_stride, void* stream);
+/* Fused projection rows [heads*(dim+rot_dim) | kv_rank | rot_dim | ...] -> cache row [normed latent | rotated key part] at
+ * slot_mapping[t], rotated query parts into qfull[t][h][kv_rank ..] (rows of kv_rank + rot_dim fp32). */
+B200_API int b200_latent_prep(int32_t f32, const void* qkv, int64_t ld, const float* norm_w, const int32_t* positions,
+                              const int32_t* slot_mapping, const float* rot, int32_t rot_dims, int64_t max_pos, float* qfull, void* cache,
+                              int32_t n_tokens, int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float eps, void* stream);
+/* y[t][h][:n_out] = W[h] x[t][h][:k] for every head; element (t, h, i) of x at x[t * ldx + h * x_hs + i], likewise y and gate
+ * (gate != NULL: y *= sigmoid(gate)).  W bf16 [heads][n_out][k]; y fp32 when y_f32. */
+B200_API int b200_head_linear(int32_t f32, int32_t y_f32, const void* x, int64_t ldx, int32_t x_hs, const void* w, void* y, int64_t ldy,
+                              int32_t y_hs, const void* gate, int64_t ldg, int32_t g_hs, int32_t n_tokens, int32_t heads, int32_t n_out,
+                              int32_t k, void* stream);
+/* b200_paged_attn_anydim with cache rows of k_row / v_row elements (0: dim / vdim; the value cache may be the key cache) and
+ * an optional per-head sink term in the softmax denominator. */
+B200_API int b200_paged_attn_anydim_ex(int32_t f32, const float* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                                       int32_t bt_stride, const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions,
+                                       void* out, int32_t n_tokens, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                                       int32_t block_size, float scale, int32_t shared_tiles, void* workspace, int32_t k_row, int32_t v_row,
+                                       const float* sink, void* stream);
+/* mLSTM: log gates [T][2 heads] (input gates, then forget gates) from w [2 heads][width] and bias; the recurrence over
+ * fused rows (q at q_off, k at k_off, v at v_off) with the state of each sequence at state + slot * slot_stride floats
+ * (b200_mlstm_state_floats per layer), out fp32 [T][heads*vdim]; then unit RMS per head, weight and sigmoid gate. */
+B200_API int b200_mlstm_gates(int32_t f32, const void* x, const void* w, const float* bias, float* out, int32_t n_tokens, int32_t width,
+                              int32_t heads, float cap, void* stream);
+B200_API int64_t b200_mlstm_state_floats(int32_t heads, int32_t dim, int32_t vdim);
+B200_API int b200_mlstm_scan(int32_t f32, const void* qkv, int64_t ld, int32_t q_off, int32_t k_off, int32_t v_off, const float* gates,
+                             const int32_t* positions, const int32_t* seq_start, const int32_t* seq_slots, float* state,
+                             int64_t slot_stride, float* out, int32_t n_seqs, int32_t heads, int32_t dim, int32_t vdim, void* stream);
+B200_API int b200_head_norm_gate(int32_t f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int32_t n_tokens,
+                                 int32_t heads, int32_t vdim, float eps, void* stream);
+/* gated: out[t][f] = act(in[t][f]) * in[t][ff + f] over rows of 2 ff; else out = act(in) (in place allowed). */
+B200_API int b200_ff_act(int32_t f32, const void* in, void* out, int32_t n_tokens, int32_t ff, int32_t gated, int32_t act, void* stream);
+/* Router without groups or bias; sigmoid_scores: scores are sigmoids of the logits instead of a softmax over the experts. */
+B200_API int b200_moe_route_scores(int32_t f32, const void* x, const void* w_router, int32_t n_tokens, int32_t width, int32_t experts,
+                                   int32_t top, int32_t sigmoid_scores, int32_t* out_ids, float* out_w, void* stream);
+/* b200_moe_experts for the other expert shapes: gated 0 = down(act(up x)) over w_up [experts][ff][width]; weight_input: the
+ * mixing weight scales the input row. */
+B200_API int b200_moe_experts_form(int32_t f32, const void* x, const void* w_up, const void* w_down, const int32_t* ids, const float* wts,
+                                   int32_t n_tokens, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts, void* ws,
+                                   int32_t gated, int32_t act, int32_t weight_input, void* stream);
 /* Router: out_ids / out_weights [T][top].  bias may be NULL. */
 B200_API int b200_moe_route(int32_t f32, const void* x, const void* w_router, const float* bias, int32_t n_tokens, int32_t width,
                    int32_t experts, int32_t top, int32_t groups, int32_t keep, int32_t* out_ids, float* out_weights, void* stream);

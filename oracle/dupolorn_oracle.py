@@ -50,20 +50,21 @@ def causal_conv(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """h [T, W], w [W, taps]: out_t = sum_j w[:, j] * h_{t - taps + 1 + j}."""
     T, taps = h.shape[0], w.shape[1]
     out = torch.zeros_like(h)
-    for t in range(T):
-        for j in range(taps):
-            s = t - taps + 1 + j
-            if s >= 0:
-                out[t] += w[:, j].to(F64) * h[s]
+    for j in range(taps):
+        back = taps - 1 - j                 # tap j reads the input `back` steps earlier
+        if back < T:
+            out[back:] += w[:, j].to(F64) * h[:T - back]
     return out
 
 
-def rotate_pairs(v: torch.Tensor, pos: int, base: float, dims: int) -> torch.Tensor:
-    """The leading `dims` entries of the last axis, pair (2i, 2i+1) turned by pos * base^(-2i/dims)."""
+def rotate_pairs(v: torch.Tensor, pos, base: float, dims: int) -> torch.Tensor:
+    """The leading `dims` entries of the last axis, pair (2i, 2i+1) turned by pos * base^(-2i/dims).  pos: a number, or a
+    tensor that broadcasts against v without its last axis."""
     out = v.clone()
+    pos = torch.as_tensor(pos, dtype=F64)
     for i in range(dims // 2):
         a = pos * base ** (-2.0 * i / dims)
-        c, s = math.cos(a), math.sin(a)
+        c, s = torch.cos(a), torch.sin(a)
         u, w = v[..., 2 * i].clone(), v[..., 2 * i + 1].clone()
         out[..., 2 * i] = u * c - w * s
         out[..., 2 * i + 1] = w * c + u * s
@@ -79,21 +80,22 @@ def latent_attention(h: torch.Tensor, m: dict, w: Dict[str, torch.Tensor], p: st
     q = (h @ f("q").T).reshape(T, H, dim + rd)
     dkv = h @ f("dkv").T
     c = rms_unit(dkv[:, :rank], eps) * f("dkv.norm")
-    kr = dkv[:, rank:]
     ku = (c @ f("uk").T).reshape(T, H, dim)
     v = (c @ f("uv").T).reshape(T, H, vd)
+    t = torch.arange(T, dtype=F64)
+    qr = rotate_pairs(q[:, :, dim:], t[:, None], base, rdims)
+    kr = rotate_pairs(dkv[:, rank:], t, base, rdims)
+    visible = torch.tril(torch.ones(T, T, dtype=torch.bool))
     out = torch.zeros(T, H, vd, dtype=F64)
-    qr = torch.stack([rotate_pairs(q[t, :, dim:], t, base, rdims) for t in range(T)])
-    krr = torch.stack([rotate_pairs(kr[t], t, base, rdims) for t in range(T)])
-    for t in range(T):
-        for hh in range(H):
-            s = (ku[: t + 1, hh] @ q[t, hh, :dim] + krr[: t + 1] @ qr[t, hh]) * m["scale"]
-            mx = s.max()
-            if sink:
-                mx = torch.maximum(mx, f("sink")[hh])
-            e = torch.exp(s - mx)
-            den = e.sum() + (torch.exp(f("sink")[hh] - mx) if sink else 0.0)
-            out[t, hh] = (e / den) @ v[: t + 1, hh]
+    for hh in range(H):
+        s = (q[:, hh, :dim] @ ku[:, hh].T + qr[:, hh] @ kr.T) * m["scale"]          # [query, key]
+        s = s.masked_fill(~visible, -math.inf)
+        mx = s.max(-1, keepdim=True).values
+        if sink:
+            mx = torch.maximum(mx, f("sink")[hh])
+        e = torch.exp(s - mx)
+        den = e.sum(-1, keepdim=True) + (torch.exp(f("sink")[hh] - mx) if sink else 0.0)
+        out[:, hh] = (e / den) @ v[:, hh]
     a = out.reshape(T, H * vd)
     if gate:
         a = a * torch.sigmoid(h @ f("g").T)
@@ -116,15 +118,14 @@ def mlstm(h: torch.Tensor, m: dict, w: Dict[str, torch.Tensor], p: str, eps: flo
     n = state.setdefault("n", torch.zeros(H, dim, dtype=F64))
     mm = state.setdefault("m", torch.zeros(H, dtype=F64))
     out = torch.zeros(T, H, vd, dtype=F64)
-    for t in range(T):
-        for hh in range(H):
-            m_new = torch.maximum(fg[t, hh] + mm[hh], ig[t, hh])
-            a, b = torch.exp(fg[t, hh] + mm[hh] - m_new), torch.exp(ig[t, hh] - m_new)
-            S[hh] = a * S[hh] + b * torch.outer(k[t, hh], v[t, hh])
-            n[hh] = a * n[hh] + b * k[t, hh]
-            mm[hh] = m_new
-            den = torch.maximum((n[hh] @ q[t, hh]).abs(), torch.exp(-m_new)) + 1e-6
-            out[t, hh] = (S[hh].T @ q[t, hh]) / den
+    for t in range(T):                       # all heads at once
+        m_new = torch.maximum(fg[t] + mm, ig[t])
+        a, b = torch.exp(fg[t] + mm - m_new), torch.exp(ig[t] - m_new)
+        S.mul_(a[:, None, None]).add_(b[:, None, None] * k[t][:, :, None] * v[t][:, None, :])
+        n.mul_(a[:, None]).add_(b[:, None] * k[t])
+        mm.copy_(m_new)
+        den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-m_new)) + 1e-6
+        out[t] = torch.einsum("hdv,hd->hv", S, q[t]) / den[:, None]
     o = rms_unit(out, eps).reshape(T, H * vd) * f("norm") * torch.sigmoid(h @ f("g").T)
     return o @ f("o").T
 
