@@ -623,6 +623,30 @@ DESIGN_SIZES = {
 }
 
 
+# Dupolorn beside Bopilorn (the closest model of the framework: a layer-list model with routed experts on the same grouped
+# linears and paged caches) at equal width, layers, heads, experts and expert width.  Dupolorn's layers alternate latent
+# attention, the mLSTM recurrence and latent attention with sink and gate; the first layer's feed-forward is dense.
+DUPOLORN_SIZES = {
+    "w2048-e32": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, r_heads=8, r_dim=128, r_vdim=256, layers=4,
+                      experts=32, top=4, ff=1024, shared=1024, dense_ff=4096, vocab=32768, kv=4, groups=4, keep=2),
+    "w1024-e16": dict(width=1024, heads=16, dim=64, rot_dim=32, vdim=64, kv_rank=256, r_heads=4, r_dim=128, r_vdim=256, layers=4,
+                      experts=16, top=2, ff=1024, shared=1024, dense_ff=2048, vocab=32768, kv=2, groups=1, keep=1),
+}
+
+
+def _dupolorn_config(Cf, name, z):
+    rot = Cf.RotarySpec(base=10000.0, dims=z["rot_dim"])
+    la = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"],
+              scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=rot)
+    mixers = [Cf.LatentAttentionSpec(**la), Cf.MLSTMSpec(heads=z["r_heads"], dim=z["r_dim"], vdim=z["r_vdim"], gate_cap=15.0),
+              Cf.LatentAttentionSpec(sink=True, gate=True, **la)]
+    moe = Cf.FeedForwardSpec(kind="moe", ff=z["ff"], act="relu2", experts=z["experts"], top=z["top"], shared_ff=z["shared"])
+    dense = Cf.FeedForwardSpec(kind="dense", ff=z["dense_ff"], act="gelu_tanh")
+    layers = [Cf.ParallelLayerSpec(mixer=mixers[i % 3], mlp=dense if i == 0 else moe) for i in range(z["layers"])]
+    return Cf.DupolornConfig(name=name, width=z["width"], vocab=z["vocab"], embed_scale=1.0, canon_taps=4, bigram_buckets=65521,
+                             bigram_mul_prev=8191, bigram_mul_cur=127, logit_softcap=30.0, layers=layers)
+
+
 def _design_batch(R, n_seqs, ctx, n_new, bs, vocab):
     """n_seqs sequences that already hold ctx tokens and bring n_new rows each; the last row of each is a logit row."""
     import numpy as np
@@ -639,6 +663,7 @@ def _design_batch(R, n_seqs, ctx, n_new, bs, vocab):
             b.row_to_seq.append(s)
         b.logit_rows.append(len(b.ids) - 1)
         b.block_tables.append(table)
+        b.seq_slots.append(s)
     return b, n_seqs * per
 
 
@@ -671,16 +696,20 @@ def run_design(args):
     sampler.start()
     t0 = time.monotonic()
     out = []
-    names = [n for n in DESIGN_SIZES if args.design_size in ("all", n)]
+    dup = args.design == "dupolorn"
+    sizes = DUPOLORN_SIZES if dup else DESIGN_SIZES
+    names = [n for n in sizes if args.design_size in ("all", n)]
     for name in names:
-        z = DESIGN_SIZES[name]
+        z = sizes[name]
         rot = Cf.RotarySpec(base=10000.0, dims=z["dim"], factor=4.0, original=4096, fast=32.0, slow=1.0, scaled=True)
         att = Cf.AttentionSpec(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, rot=rot,
                                value_rot=Cf.RotarySpec(base=10000.0, dims=z["dim"]))
         moe = Cf.MoESpec(experts=z["experts"], top=z["top"], ff=z["ff"], groups=z["groups"], keep=z["keep"])
         arms = {"bopilorn": Cf.BopilornConfig(name=name, width=z["width"], vocab=z["vocab"], embed_scale=1.0,
                                               layers=[Cf.StackLayerSpec(mixer=att, mlp=moe) for _ in range(z["layers"])])}
-        if z["dim"] == 128:
+        if dup:
+            arms = {"dupolorn": _dupolorn_config(Cf, name, z), "bopilorn": arms["bopilorn"]}
+        elif z["dim"] == 128:
             arms["llama"] = Cf.ModelConfig(name=name, hidden=z["width"], n_layers=z["layers"], n_q_heads=z["heads"], n_kv_heads=z["kv"],
                                            intermediate=z["top"] * z["ff"], vocab=z["vocab"], max_pos=8192)
         rec = {"size": name, "shape": z, "ms": {}, "tok_s": {}}
@@ -688,7 +717,7 @@ def run_design(args):
             bs = 128
             cases = {"prefill_2048": (1, 0, 2048), "decode_b64_ctx512": (64, 512, 1), "decode_b1_ctx512": (1, 512, 1)}
             n_blocks = 64 * 5 + 8
-            r = R.make_runner(cfg, max_tokens=2048, max_model_len=4096, block_size=bs, n_blocks=n_blocks)
+            r = R.make_runner(cfg, max_tokens=2048, max_model_len=4096, block_size=bs, n_blocks=n_blocks, n_state_slots=65)
             r.init_random_weights(seed=7)
             rec["ms"][arm], rec["tok_s"][arm] = {}, {}
             for case, (n_seqs, ctx, n_new) in cases.items():
@@ -704,7 +733,8 @@ def run_design(args):
             torch.cuda.empty_cache()
         out.append(rec)
     clocks = sampler.stop(t0, time.monotonic())
-    emit({"metric": "design_compare", "design": "Bopilorn", "closest": "llama (fixed decoder stack)", "dtype": "bf16",
+    emit({"metric": "design_compare", "design": "Dupolorn" if dup else "Bopilorn",
+          "closest": "bopilorn (layer-list model with routed experts)" if dup else "llama (fixed decoder stack)", "dtype": "bf16",
           "data": "synthetic, random-init weights", "steps": K, "warmup": W, "l2": "flushed between steps (512 MiB written)",
           "sizes": out, "clocks": clocks})
 
@@ -718,10 +748,10 @@ def main():
     ap.add_argument("--workload", default="llama8b-bs64", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true", help="skip the `also` and `tp` sections of the default run")
-    ap.add_argument("--design", default=None, choices=["bopilorn"],
+    ap.add_argument("--design", default=None, choices=["bopilorn", "dupolorn"],
                     help="instead of the default workload: prefill / decode throughput of this design beside the closest fixed-stack "
                          "model at equal size")
-    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(DESIGN_SIZES))
+    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(set(DESIGN_SIZES) | set(DUPOLORN_SIZES)))
     args = ap.parse_args()
     claim_stdout()
     if args.design:

@@ -405,9 +405,11 @@ moe_group_kernel(const int32_t* __restrict__ ids, int n_pairs, int experts, int 
 }
 
 // xg[row] = x[row_pair[row] / top] (zeros for padding rows); rows of unused tiles are left alone.  width % 8 == 0.
+// in_wts given (the mixing weight belongs to the expert's input): the row is scaled by its pair's weight (fp32 product,
+// rounded once), and ones[pair] = 1 so that the closing linear's per-pair factor is neutral.
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ row_pair,
-                  int N, int top, int width, __nv_bfloat16* __restrict__ xg) {
+                  int N, int top, int width, __nv_bfloat16* __restrict__ xg, const float* __restrict__ in_wts, float* __restrict__ ones) {
   pdl_wait();
   pdl_launch_dependents();
   const int row = blockIdx.x;
@@ -420,7 +422,17 @@ moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict
     return;
   }
   const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(pair / top) * width);
-  for (int c = threadIdx.x; c < chunks; c += 128) dst[c] = __ldg(src + c);
+  if (in_wts == nullptr) {
+    for (int c = threadIdx.x; c < chunks; c += 128) dst[c] = __ldg(src + c);
+    return;
+  }
+  const float wt = in_wts[pair];
+  if (threadIdx.x == 0) ones[pair] = 1.0f;
+  for (int c = threadIdx.x; c < chunks; c += 128) {
+    const uint4 v = __ldg(src + c);
+    dst[c] = make_uint4(pack_bf16(bf16lo(v.x) * wt, bf16hi(v.x) * wt), pack_bf16(bf16lo(v.y) * wt, bf16hi(v.y) * wt),
+                        pack_bf16(bf16lo(v.z) * wt, bf16hi(v.z) * wt), pack_bf16(bf16lo(v.w) * wt, bf16hi(v.w) * wt));
+  }
 }
 
 }  // namespace
@@ -442,14 +454,15 @@ int64_t moe_workspace_bytes(int T, int top, int experts, int width, int ff) {
   int64_t b = al256(((int64_t)T * top + experts + 8) * 4);
   if (width > 0 && ff > 0 && moe_tc_supported(width, ff)) {
     const int64_t rows = (int64_t)T * top + (int64_t)experts * 128, tiles = (int64_t)T * top / 16 + experts + 1;
-    b = std::max(b, al256(tiles * 4) + al256(rows * 4) + al256(rows * width * 2) + al256(rows * 2 * ff * 2) + al256(rows * ff * 2));
+    b = std::max(b, al256(tiles * 4) + al256(rows * 4) + al256(rows * width * 2) + al256(rows * 2 * ff * 2) + al256(rows * ff * 2) +
+                        al256((int64_t)T * top * 4));
   }
   return b;
 }
 
 static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
                           const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws,
-                          cudaStream_t s) {
+                          cudaStream_t s, ExpertForm form) {
   int N, n_tiles;
   moe_tc_shape(T, top, experts, &N, &n_tiles);
   const int64_t rows = (int64_t)n_tiles * N;
@@ -463,6 +476,8 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
   __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p);
   p += al256(rows * 2 * ff * 2);
   __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p);
+  p += al256(rows * ff * 2);
+  float* ones = reinterpret_cast<float*>(p);
   const size_t smem_grp = (size_t)experts * (1 + kGroupWarps) * 4;
   B200_REQUIRE(smem_grp <= 200 * 1024, B200_ERR_UNSUPPORTED, "experts: %d experts exceed the grouping kernel", experts);
   static bool done_grp[64] = {};
@@ -470,10 +485,22 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
   B200_CUDA(launch(moe_group_kernel, dim3(1), dim3(kGroupThreads), smem_grp, s, ids, T * top, experts, N, n_tiles,
                    tile_expert, row_pair));
   B200_CUDA(launch(moe_gather_kernel, dim3((unsigned)rows), dim3(128), (size_t)0, s, x, (const int32_t*)tile_expert,
-                   (const int32_t*)row_pair, N, top, width, xg));
+                   (const int32_t*)row_pair, N, top, width, xg, form.weight_input ? wts : (const float*)nullptr, ones));
+  if (form.weight_input) wts = ones;
   int rc;
   static const int fuse_env = getenv("B200_MOE_FUSE_SILU") ? atoi(getenv("B200_MOE_FUSE_SILU")) : 1;
-  if (fuse_env && ff % 64 == 0 && (N <= 64 || fuse_env > 1)) {
+  if (!form.gated) {
+    // one projection, activated in place
+    rc = linear_tc_grouped(xg, width, N, n_tiles, w_gu, experts, ff, width, tile_expert, act, ff, nullptr, nullptr, nullptr, s);
+    if (rc) return rc;
+    rc = ff_act(false, act, act, (int)rows, ff, false, form.act, s);
+    if (rc) return rc;
+  } else if (form.act != B200_ACT_SILU) {
+    rc = linear_tc_grouped(xg, width, N, n_tiles, w_gu, experts, 2 * ff, width, tile_expert, gu, 2 * ff, nullptr, nullptr, nullptr, s);
+    if (rc) return rc;
+    rc = ff_act(false, gu, act, (int)rows, ff, true, form.act, s);
+    if (rc) return rc;
+  } else if (fuse_env && ff % 64 == 0 && (N <= 64 || fuse_env > 1)) {
     // gate and up rows of a slab come in as two 64-row boxes; the epilogue activates (as the dense gate|up linear does).
     // Decode-sized tiles only: at 128 tokens per tile the epilogue's exponentials cost more than the pass they save
     // (measured: 145 us against 119 + 19 us for 8192 rows of width 2048 into ff 1024)
@@ -560,9 +587,8 @@ int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_b
                 ExpertForm form) {
   if (T == 0) return B200_OK;
   static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
-  const bool first_form = form.gated && form.act == B200_ACT_SILU && !form.weight_input;
-  if (!f32 && tc_env && ws && moe_tc_supported(width, ff) && first_form)
-    return moe_experts_tc((const __nv_bfloat16*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, s);
+  if (!f32 && tc_env && ws && moe_tc_supported(width, ff))
+    return moe_experts_tc((const __nv_bfloat16*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, s, form);
   // an expert is chosen at most once per token, so it has at most T tokens: ceil(T / 16) tiles bound every expert
   const bool grouped = (int64_t)T * top >= 4 * (int64_t)experts && T >= 64;
   return f32 ? moe_experts_t<float>((const float*)x, w_gu, w_down, ids, wts, T, width, ff, experts, top, parts, ws, grouped, s, form)

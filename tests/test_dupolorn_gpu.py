@@ -316,24 +316,29 @@ def test_sigmoid_router_against_the_oracle(f32, T, W, experts, top):
 
 
 @pytest.mark.parametrize("f32", [1, 0])
-@pytest.mark.parametrize("T,W,ff,experts,top", [(5, 72, 40, 6, 2), (150, 96, 24, 4, 3), (70, 64, 130, 3, 1), (260, 100, 36, 5, 2)])
+@pytest.mark.parametrize("T,W,ff,experts,top", [(5, 72, 40, 6, 2), (150, 96, 24, 4, 3), (70, 64, 130, 3, 1), (260, 100, 36, 5, 2),
+                                                (1, 64, 64, 8, 2), (700, 128, 72, 3, 1), (3000, 64, 64, 4, 3)])
 def test_ungated_experts_with_the_weight_on_their_input(f32, T, W, ff, experts, top):
+    """The CUDA-core token and grouped forms (32-bit mode; sizes no vector access fits) and the grouped tensor-core form (bf16
+    with width and ff multiples of 8: every token-tile size, experts nobody chose)."""
     g = torch.Generator().manual_seed(T + ff)
     adt = torch.float32 if f32 else torch.bfloat16
     x = torch.randn(T, W, generator=g).to(adt).float()
     up = U.bf16_exact(torch.randn(experts, ff, W, generator=g) * W ** -0.5)
     down = U.bf16_exact(torch.randn(experts, W, ff, generator=g) * ff ** -0.5)
     ids = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(T)]).to(torch.int32)
-    wts = torch.rand(T, top, generator=g) * 0.9 + 0.05
+    wts = torch.rand(T, top, generator=g) * 0.9 + 0.05      # NOT a factor of the output: relu(w z)^2 = w^2 relu(z)^2
+    if top == 1:
+        ids[ids == experts - 1] = 0        # the last expert gets no token
     want = torch.stack([torch.stack([O.relu2_expert(wts[t, k].double() * x[t].double(), up[ids[t, k]], down[ids[t, k]]) for k in range(top)])
                         for t in range(T)])
-    # the weight is NOT a factor of the output: relu(w z)^2 = w^2 relu(z)^2
-    ws = torch.zeros(int(lib().b200_moe_workspace_bytes(T, top, experts, 0, ff)), dtype=torch.uint8, device=DEV)
-    parts = torch.zeros(T, top, W, device=DEV)
+    ws = torch.zeros(int(lib().b200_moe_workspace_bytes(T, top, experts, W, ff)), dtype=torch.uint8, device=DEV)
+    parts = torch.full((T, top, W), float("nan"), device=DEV)
     check(lib().b200_moe_experts_form(f32, dev(x, adt).data_ptr(), dev(up, torch.bfloat16).data_ptr(), dev(down, torch.bfloat16).data_ptr(),
                                       dev(ids).data_ptr(), dev(wts).data_ptr(), T, W, ff, experts, top, parts.data_ptr(), ws.data_ptr(), 0, 2, 1,
                                       None))
     sync()
+    assert torch.isfinite(parts).all()
     assert torch.allclose(parts.cpu().double(), want, atol=2e-5 if f32 else 3e-2, rtol=1e-5 if f32 else 3e-2)
 
 
