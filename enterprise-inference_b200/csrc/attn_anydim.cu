@@ -283,6 +283,15 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
 
 int64_t paged_attn_anydim_workspace_bytes(int T) { return ((int64_t)2 * T + 8) * 4; }
 
+// The run list of a step in ws (n_runs at ws[0], (first row, rows) pairs from ws[8]): what plan = 1 builds, as a call of its
+// own for the kernels that share it.
+int paged_attn_runs_plan(const int32_t* row_to_seq, const int32_t* ctx_lens, int T, void* ws, cudaStream_t s) {
+  int32_t* runs = static_cast<int32_t*>(ws) + 8;
+  int32_t* n_runs = static_cast<int32_t*>(ws);
+  B200_CUDA(launch(attn_runs_plan_kernel, dim3(1), dim3(32), (size_t)0, s, row_to_seq, ctx_lens, T, runs, n_runs));
+  return B200_OK;
+}
+
 template <typename CT, typename AT>
 static int paged_attn_anydim_t(const float* q, const void* kc, const void* vc, const int32_t* block_table, int bt_stride,
                                const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, const float* vrot,

@@ -1,0 +1,240 @@
+// Paged causal attention over latent cache rows on the tensor cores (bf16 serving mode of B200_MIXER_LATENT).
+//
+// One kv head serves every query head, and a key row's leading `rank` entries are its value, so all heads of a token share
+// every byte of the cache: a CTA takes 16 (row, head) pairs of one run of consecutive rows of a sequence and walks the
+// context in tiles of 64 keys.  Per tile the key rows are gathered once into shared memory (cp.async, 16-byte chunks through
+// the block table), S = Q K^T and O += P V run as bf16 mma.sync m16n8k16 with fp32 accumulators, and the softmax between
+// them is fp32: scores scaled and masked per pair (a pair sees keys below its own context length), running maximum and sum
+// per pair, weights rounded to bf16 only as the second product's operand.  An optional per-head sink joins the denominator
+// at the end.  Warp w owns keys 16w..16w+15 of a tile for the scores and value columns 16(w + 4g) .. for the output.
+//
+// Queries come as fp32 rows [T][heads][krow] (rounded to bf16 when staged); output rows are bf16 [T][heads][rank].
+// Shapes: krow and rank multiples of 16, rank <= 512.  Everything else (and the 32-bit mode) takes attn_anydim.cu; both walk
+// the same cache and the same run list, and agree within bf16 rounding of the operands.
+#include <stdlib.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kLaKeys = 64, kLaPairs = 16, kLaThreads = 128;
+constexpr int kSsStride = kLaKeys + 4;    // fp32 score rows
+constexpr int kPsStride = kLaKeys + 8;    // bf16 weight rows (144 bytes: 16-byte aligned, conflict-free for ldmatrix)
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float& c0, float& c1, float& c2, float& c3, const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+template <int NG>   // 16-column output groups per warp: rank <= 64 NG
+__global__ void __launch_bounds__(kLaThreads)
+latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const int32_t* __restrict__ block_table,
+                       int bt_stride, const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ ctx_lens,
+                       __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ runs, const int32_t* __restrict__ n_runs, int heads,
+                       int krow, int rank, int block_size, float scale, const float* __restrict__ sink) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int item = blockIdx.x, chunk = blockIdx.y;
+  if (item >= *n_runs) return;
+  const int t0 = runs[2 * item], nr = runs[2 * item + 1];
+  const int nq = nr * heads, i0 = chunk * kLaPairs;
+  if (i0 >= nq) return;
+  const int ks = krow + 8;   // bf16 elements per staged row: 16-byte aligned, 4 words off a bank multiple
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);      // [64][ks]
+  __nv_bfloat16* Qs = Ks + kLaKeys * ks;                            // [16][ks]
+  float* Ss = reinterpret_cast<float*>(Qs + kLaPairs * ks);         // [16][68]
+  __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + kLaPairs * kSsStride);   // [16][72]
+  float* corr = reinterpret_cast<float*>(Ps + kLaPairs * kPsStride);                 // [16]
+  float* mrow = corr + kLaPairs;
+  float* lrow = mrow + kLaPairs;
+  int* ctxp = reinterpret_cast<int*>(lrow + kLaPairs);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < kLaPairs) {
+    const int i = i0 + tid;
+    ctxp[tid] = i < nq ? ctx_lens[t0 + i / heads] : 0;
+    mrow[tid] = -INFINITY;
+    lrow[tid] = 0.f;
+  }
+  for (int e = tid; e < kLaPairs * krow; e += kLaThreads) {
+    const int p = e / krow, d = e % krow, i = i0 + p;
+    Qs[p * ks + d] = __float2bfloat16_rn(i < nq ? q[((int64_t)(t0 + i / heads) * heads + i % heads) * krow + d] : 0.f);
+  }
+  const int last_row = min(nr - 1, (i0 + kLaPairs - 1) / heads);
+  const int ctx_max = ctx_lens[t0 + last_row];
+  const int32_t* bt = block_table + (int64_t)(row_to_seq ? row_to_seq[t0] : t0) * bt_stride;
+  const int cpr = krow >> 3;   // 16-byte chunks per row
+  float o[NG][8];
+#pragma unroll
+  for (int g = 0; g < NG; ++g)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[g][j] = 0.f;
+  __syncthreads();
+
+  for (int base = 0; base < ctx_max; base += kLaKeys) {
+    const int n = min(kLaKeys, ctx_max - base);
+    for (int e = tid; e < kLaKeys * cpr; e += kLaThreads) {
+      const int r = e / cpr, c = e % cpr;
+      __nv_bfloat16* dst = Ks + r * ks + c * 8;
+      if (r < n) {
+        const int j = base + r;
+        cp_async16(dst, kc + ((int64_t)bt[j / block_size] * block_size + j % block_size) * krow + c * 8);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);   // rows past the context: finite values under zero weights
+      }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // scores of this warp's 16 keys for all 16 pairs
+    {
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const __nv_bfloat16* ap = Qs + (lane & 15) * ks + (lane >> 4) * 8;
+      const __nv_bfloat16* bp = Ks + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * ks + ((lane >> 3) & 1) * 8;
+      for (int k0 = 0; k0 < krow; k0 += 16) {
+        uint32_t a[4], b[4];
+        ldsm_x4(a, ap + k0);
+        ldsm_x4(b, bp + k0);
+        mma_bf16(s[0][0], s[0][1], s[0][2], s[0][3], a, b[0], b[1]);
+        mma_bf16(s[1][0], s[1][1], s[1][2], s[1][3], a, b[2], b[3]);
+      }
+      const int row = lane >> 2, col = warp * 16 + (lane & 3) * 2;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        Ss[row * kSsStride + col + nt * 8] = s[nt][0];
+        Ss[row * kSsStride + col + nt * 8 + 1] = s[nt][1];
+        Ss[(row + 8) * kSsStride + col + nt * 8] = s[nt][2];
+        Ss[(row + 8) * kSsStride + col + nt * 8 + 1] = s[nt][3];
+      }
+    }
+    __syncthreads();
+    // softmax bookkeeping: this warp's 4 pairs, two keys per lane
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+      const int row = warp * 4 + rr, c = ctxp[row];
+      const int j0 = base + lane, j1 = j0 + 32;
+      const float s0 = j0 < c ? Ss[row * kSsStride + lane] * scale : -INFINITY;
+      const float s1 = j1 < c ? Ss[row * kSsStride + lane + 32] * scale : -INFINITY;
+      const float m_old = mrow[row];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+      float p0 = 0.f, p1 = 0.f, cr = 1.f;
+      if (m_new != -INFINITY) {
+        p0 = j0 < c ? expf(s0 - m_new) : 0.f;
+        p1 = j1 < c ? expf(s1 - m_new) : 0.f;
+        cr = expf(m_old - m_new);
+      }
+      const float sum = warp_sum(p0 + p1);
+      Ps[row * kPsStride + lane] = __float2bfloat16_rn(p0);
+      Ps[row * kPsStride + lane + 32] = __float2bfloat16_rn(p1);
+      __syncwarp();
+      if (lane == 0) {
+        mrow[row] = m_new;
+        lrow[row] = lrow[row] * cr + sum;
+        corr[row] = cr;
+      }
+    }
+    __syncthreads();
+    // O = O * corr + P V over this warp's column groups
+    {
+      const float c_lo = corr[lane >> 2], c_hi = corr[(lane >> 2) + 8];
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        o[g][0] *= c_lo; o[g][1] *= c_lo; o[g][4] *= c_lo; o[g][5] *= c_lo;
+        o[g][2] *= c_hi; o[g][3] *= c_hi; o[g][6] *= c_hi; o[g][7] *= c_hi;
+      }
+      const __nv_bfloat16* ap = Ps + (lane & 15) * kPsStride + (lane >> 4) * 8;
+      const __nv_bfloat16* vp = Ks + ((lane & 7) + ((lane >> 3) & 1) * 8) * ks + (lane >> 4) * 8;
+#pragma unroll
+      for (int kk = 0; kk < kLaKeys / 16; ++kk) {
+        uint32_t a[4];
+        ldsm_x4(a, ap + kk * 16);
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          const int col0 = (warp + 4 * g) * 16;
+          if (col0 < rank) {
+            uint32_t b[4];
+            ldsm_x4_t(b, vp + kk * 16 * ks + col0);
+            mma_bf16(o[g][0], o[g][1], o[g][2], o[g][3], a, b[0], b[1]);
+            mma_bf16(o[g][4], o[g][5], o[g][6], o[g][7], a, b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // finish: sink, normalise, store
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int p = (lane >> 2) + half * 8, i = i0 + p;
+    if (i >= nq) continue;
+    const int t = t0 + i / heads, h = i % heads;
+    float l = lrow[p], osc = 1.f;
+    if (sink != nullptr) {
+      const float m = mrow[p], sk = sink[h], mn = fmaxf(m, sk);
+      osc = expf(m - mn);
+      l = l * osc + expf(sk - mn);
+    }
+    const float inv = l > 0.f ? osc / l : 0.f;
+    __nv_bfloat16* dst = out + ((int64_t)t * heads + h) * rank;
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      const int col0 = (warp + 4 * g) * 16;
+      if (col0 < rank) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int col = col0 + nt * 8 + (lane & 3) * 2;
+          *reinterpret_cast<__nv_bfloat162*>(dst + col) =
+              __floats2bfloat162_rn(o[g][nt * 4 + half * 2] * inv, o[g][nt * 4 + half * 2 + 1] * inv);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+bool latent_attn_mma_supported(int heads, int krow, int rank) {
+  static const int env = getenv("B200_LATENT_MMA") ? atoi(getenv("B200_LATENT_MMA")) : 1;
+  const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 16);
+  return env && heads > 0 && krow % 16 == 0 && rank % 16 == 0 && rank > 0 && rank <= 512 && rank <= krow && smem <= 200 * 1024;
+}
+
+// runs / n_runs: the run list of the step (attn_anydim.cu builds it: runs of at most 16 consecutive rows of one sequence)
+int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* block_table, int bt_stride, const int32_t* row_to_seq,
+                    const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
+                    int rank, int block_size, float scale, const float* sink, cudaStream_t s) {
+  if (T == 0) return B200_OK;
+  B200_REQUIRE(latent_attn_mma_supported(heads, krow, rank), B200_ERR_UNSUPPORTED, "latent_attn_mma: shape %d / %d / %d", heads, krow, rank);
+  B200_REQUIRE(reinterpret_cast<uintptr_t>(kc) % 16 == 0, B200_ERR_INVALID, "latent_attn_mma: cache not 16-byte aligned");
+  const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 16);
+  const dim3 grid(T, (16 * heads + kLaPairs - 1) / kLaPairs), block(kLaThreads);
+#define LA(NGV)                                                                                                                     \
+  do {                                                                                                                              \
+    static bool done[64] = {};                                                                                                      \
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(latent_attn_mma_kernel<NGV>, 200 * 1024, done));                            \
+    B200_CUDA(launch(latent_attn_mma_kernel<NGV>, grid, block, smem, s, q, kc, block_table, bt_stride, row_to_seq, ctx_lens, out, runs, \
+                     n_runs, heads, krow, rank, block_size, scale, sink));                                                          \
+  } while (0)
+  if (rank <= 64) LA(1);
+  else if (rank <= 128) LA(2);
+  else if (rank <= 256) LA(4);
+  else LA(8);
+#undef LA
+  return B200_OK;
+}
+
+}  // namespace b200

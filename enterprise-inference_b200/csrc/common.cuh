@@ -299,6 +299,12 @@ int paged_attn_anydim(bool f32, const float* q, const void* kc, const void* vc, 
                       int plan, void* ws, cudaStream_t s, int kstride = 0, int vstride = 0, const float* sink = nullptr);
 // kstride / vstride: elements per cache row when they exceed dim / vdim (0: dim / vdim; the value cache may then be the key
 // cache itself, a value being the leading vdim entries of the row); sink [heads]: exp(sink[h]) joins the softmax denominator
+int paged_attn_runs_plan(const int32_t* row_to_seq, const int32_t* ctx_lens, int T, void* ws, cudaStream_t s);
+// latent cache rows on the tensor cores (attn_latent.cu): bf16 cache, fp32 queries, bf16 output [T][heads][rank]
+bool latent_attn_mma_supported(int heads, int krow, int rank);
+int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* block_table, int bt_stride, const int32_t* row_to_seq,
+                    const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
+                    int rank, int block_size, float scale, const float* sink, cudaStream_t s);
 // mixture of experts (moe.cu)
 int64_t moe_workspace_bytes(int T, int top, int experts, int width, int ff);
 bool moe_tc_supported(int width, int ff);

@@ -207,6 +207,7 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
   int attn_plan = (a.row_to_seq && T >= 32 && T >= 2 * S) ? 1 : 0;
   static const int plan_env = getenv("B200_STACK_ATTN_RUNS") ? atoi(getenv("B200_STACK_ATTN_RUNS")) : 1;
   if (!plan_env) attn_plan = 0;
+  bool runs_built = false;   // the step's run list is in the attention workspace
   const int64_t rstride = (int64_t)m.max_tokens * Wd;
   float* u = M->x;
   int32_t* st_prev = reinterpret_cast<int32_t*>(M->state);
@@ -237,10 +238,20 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
       // q' = W_uk^T q_plain into the leading kv_rank entries of every query row
       STEP(head_linear(f32, true, M->qkv, qr, qh, W.uk_t, M->q, (int64_t)L.heads * krow, krow, nullptr, 0, 0, T, L.heads, L.kv_rank,
                        L.dim, s));
-      STEP(paged_attn_anydim(f32, M->q, W.kc, W.kc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
-                             M->lat, T, L.heads, 1, krow, L.kv_rank, m.block_size, L.scale, attn_plan, M->attn_ws, s, krow, krow,
-                             (L.mixer_flags & B200_MIXF_SINK) ? W.sink : nullptr));
-      if (attn_plan == 1) attn_plan = 2;
+      const float* sink = (L.mixer_flags & B200_MIXF_SINK) ? W.sink : nullptr;
+      if (!f32 && latent_attn_mma_supported(L.heads, krow, L.kv_rank)) {
+        if (attn_plan != 2 && !runs_built) STEP(paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s));
+        runs_built = true;
+        if (attn_plan == 1) attn_plan = 2;
+        STEP(latent_attn_mma(M->q, (const __nv_bfloat16*)W.kc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens,
+                             (__nv_bfloat16*)M->lat, static_cast<const int32_t*>(M->attn_ws) + 8, static_cast<const int32_t*>(M->attn_ws), T,
+                             L.heads, krow, L.kv_rank, m.block_size, L.scale, sink, s));
+      } else {
+        STEP(paged_attn_anydim(f32, M->q, W.kc, W.kc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
+                               M->lat, T, L.heads, 1, krow, L.kv_rank, m.block_size, L.scale, runs_built && attn_plan == 1 ? 2 : attn_plan,
+                               M->attn_ws, s, krow, krow, sink));
+        if (attn_plan == 1) attn_plan = 2, runs_built = true;
+      }
       const bool gate = (L.mixer_flags & B200_MIXF_GATE) != 0;
       const char* gptr = static_cast<const char*>(M->qkv) + (int64_t)(L.heads * qh + krow) * es;
       STEP(head_linear(f32, false, M->lat, (int64_t)L.heads * L.kv_rank, L.kv_rank, W.uv, M->attn, av, L.vdim, gate ? gptr : nullptr, qr,
@@ -982,4 +993,17 @@ extern "C" int b200_moe_experts_form(int32_t f32, const void* x, const void* w_u
   form.weight_input = weight_input != 0;
   return moe_experts(f32 != 0, x, (const __nv_bfloat16*)w_up, (const __nv_bfloat16*)w_down, ids, wts, T, width, ff, experts, top, parts, ws,
                      (cudaStream_t)stream, form);
+}
+
+extern "C" int b200_latent_attn_supported(int32_t heads, int32_t k_row, int32_t rank) { return latent_attn_mma_supported(heads, k_row, rank) ? 1 : 0; }
+
+extern "C" int b200_latent_attn(const float* q, const void* cache, const int32_t* block_table, int32_t bt_stride, const int32_t* row_to_seq,
+                                const int32_t* ctx_lens, void* out, int32_t T, int32_t heads, int32_t k_row, int32_t rank,
+                                int32_t block_size, float scale, const float* sink, void* workspace, void* stream) {
+  B200_REQUIRE(q && cache && block_table && ctx_lens && out && workspace && block_size > 0, B200_ERR_INVALID, "latent_attn: bad argument");
+  int rc = paged_attn_runs_plan(row_to_seq, ctx_lens, T, workspace, (cudaStream_t)stream);
+  if (rc) return rc;
+  return latent_attn_mma(q, (const __nv_bfloat16*)cache, block_table, bt_stride, row_to_seq, ctx_lens, (__nv_bfloat16*)out,
+                         static_cast<const int32_t*>(workspace) + 8, static_cast<const int32_t*>(workspace), T, heads, k_row, rank,
+                         block_size, scale, sink, (cudaStream_t)stream);
 }

@@ -191,6 +191,40 @@ def test_attention_over_latent_rows_sink_far_keys_and_block_borders(f32, heads, 
     assert torch.allclose(out.float().cpu().double(), want, atol=2e-5 if f32 else 2e-2, rtol=0 if f32 else 2e-2)
 
 
+@pytest.mark.parametrize("heads,rank,rd,with_sink", [(3, 32, 16, True), (6, 128, 32, False), (16, 512, 64, True), (20, 64, 0, True), (1, 16, 16, False)])
+def test_latent_attention_on_the_tensor_cores(heads, rank, rd, with_sink):
+    """Decode rows and runs of consecutive rows (pairs of one CTA with different context lengths; more heads than a CTA holds
+    pairs), contexts around tile (64) and block borders, a key far back that decides two rows, the sink."""
+    g = torch.Generator().manual_seed(rank + heads)
+    bs, n_tok, scale, krow = 16, 600, 0.25, rank + rd
+    assert lib().b200_latent_attn_supported(heads, krow, rank) == 1 and lib().b200_latent_attn_supported(heads, krow + 8, rank) == 0
+    nb = (n_tok + bs - 1) // bs
+    rows = torch.randn(n_tok, krow, generator=g).to(torch.bfloat16).float()
+    perm = torch.randperm(nb + 4, generator=g)[:nb]
+    kc = torch.zeros(nb + 4, 1, bs, krow, dtype=torch.bfloat16)
+    for j in range(n_tok):
+        kc[perm[j // bs], 0, j % bs] = rows[j].to(torch.bfloat16)
+    ctxs = [1, 2, 3, 15, 16, 17, 63, 64, 65, 127, 128, 129, 600, 560] + list(range(1, 40)) + list(range(565, 600))
+    seq = [i for i in range(14)] + [14] * 39 + [15] * 35        # 14 decode rows of their own, then two runs (the table is shared)
+    T, far = len(ctxs), 5
+    q = torch.randn(T, heads, krow, generator=g).to(torch.bfloat16).float()
+    for r in (12, 13):
+        q[r] = (rows[far][None, :] * (40.0 / scale / krow)).to(torch.bfloat16).float()
+    sink = (torch.randn(heads, generator=g) * 2.0 + 1.0) if with_sink else None
+    want = torch.stack([_latent_scores_oracle(q[t].double(), rows.double(), ctxs[t], rank, scale, sink.double() if with_sink else None)
+                        for t in range(T)])
+    assert torch.allclose(want[12], rows[far, :rank].double().expand(heads, rank), atol=5e-2)
+    ws = torch.zeros(int(lib().b200_paged_attn_anydim_workspace_bytes(T)), dtype=torch.uint8, device=DEV)
+    bt = perm.to(torch.int32)[None, :].repeat(16, 1).contiguous()
+    out = torch.full((T, heads, rank), float("nan"), dtype=torch.bfloat16, device=DEV)
+    check(lib().b200_latent_attn(dev(q).data_ptr(), dev(kc).data_ptr(), dev(bt).data_ptr(), nb, i32(seq).data_ptr(), i32(ctxs).data_ptr(),
+                                 out.data_ptr(), T, heads, krow, rank, bs, scale, dev(sink).data_ptr() if with_sink else None, ws.data_ptr(),
+                                 None))
+    sync()
+    assert torch.isfinite(out.float()).all()
+    assert torch.allclose(out.float().cpu().double(), want, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("f32", [1, 0])
 @pytest.mark.parametrize("heads,dim,rd,rot_dims,rank,vdim,gate", [(3, 24, 16, 16, 40, 20, True), (2, 16, 24, 8, 28, 36, False), (5, 70, 2, 2, 9, 3, True)])
 def test_latent_rows_rotation_and_the_per_head_expansions(f32, heads, dim, rd, rot_dims, rank, vdim, gate):
