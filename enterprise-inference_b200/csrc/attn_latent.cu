@@ -88,14 +88,17 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
 
   for (int base = 0; base < ctx_max; base += kLaKeys) {
     const int n = min(kLaKeys, ctx_max - base);
-    for (int e = tid; e < kLaKeys * cpr; e += kLaThreads) {
-      const int r = e / cpr, c = e % cpr;
-      __nv_bfloat16* dst = Ks + r * ks + c * 8;
+    {
+      // two threads per key row, alternate 16-byte chunks: one block-table lookup per thread and tile
+      const int r = tid >> 1;
+      __nv_bfloat16* dst = Ks + r * ks;
       if (r < n) {
         const int j = base + r;
-        cp_async16(dst, kc + ((int64_t)bt[j / block_size] * block_size + j % block_size) * krow + c * 8);
+        const __nv_bfloat16* src = kc + ((int64_t)bt[j / block_size] * block_size + j % block_size) * krow;
+        for (int c = tid & 1; c < cpr; c += 2) cp_async16(dst + c * 8, src + c * 8);
       } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);   // rows past the context: finite values under zero weights
+        // rows past the context: finite values under zero weights
+        for (int c = tid & 1; c < cpr; c += 2) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     cp_async_wait_all();

@@ -10,6 +10,8 @@
 //    part (interleaved pairs, fp32 cos|sin table), cache append, rotated query parts into the fp32 query rows;
 //  * head_linear: y[t][h] = W[h] x[t][h] for every head at once, strided rows in and out, fp32 accumulation, optional
 //    sigmoid gate on the output (the output gate of the mixer reads the same input as the projections).
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -103,6 +105,101 @@ head_linear_kernel(const AT* __restrict__ x, int64_t ldx_, int x_hs, const __nv_
   }
 }
 
+// ---- the same per-head products on the tensor cores (bf16 inputs, inner size a multiple of 16) --------------------------------
+// CTA = (64 rows, head, 64 outputs); warp w owns rows 16w .. 16w + 15.  Inputs and the head's weight rows are staged in
+// shared memory in inner chunks of 128 (16-byte copies when the input rows allow it) and multiplied as bf16 mma.sync
+// m16n8k16 with fp32 accumulators; the epilogue applies the optional sigmoid gate and stores fp32 or bf16.
+constexpr int kHmRows = 64, kHmOuts = 64, kHmChunk = 128, kHmStride = kHmChunk + 8;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float& c0, float& c1, float& c2, float& c3, const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename YT, bool VEC>
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx_, int x_hs, const __nv_bfloat16* __restrict__ w, YT* __restrict__ y,
+                       int64_t ldy, int y_hs, const __nv_bfloat16* __restrict__ gate, int64_t ldg, int g_hs, int T, int n_out, int k) {
+  __shared__ __align__(16) __nv_bfloat16 Xs[kHmRows * kHmStride];
+  __shared__ __align__(16) __nv_bfloat16 Ws[kHmOuts * kHmStride];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t0 = blockIdx.x * kHmRows, h = blockIdx.y, o0 = blockIdx.z * kHmOuts;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const __nv_bfloat16* wh = w + ((int64_t)h * n_out + o0) * k;
+  for (int k0 = 0; k0 < k; k0 += kHmChunk) {
+    const int kc = min(kHmChunk, k - k0), cpr = kc >> 3;
+    // two threads per row (input rows and weight rows alike), alternate 16-byte chunks
+    const int r = tid >> 1;
+    {
+      const bool live = t0 + r < T;
+      const __nv_bfloat16* src = x + (int64_t)(t0 + r) * ldx_ + (int64_t)h * x_hs + k0;
+      __nv_bfloat16* dst = Xs + r * kHmStride;
+      for (int c = tid & 1; c < cpr; c += 2) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (live) {
+          if (VEC) {
+            v = __ldg(reinterpret_cast<const uint4*>(src + c * 8));
+          } else {
+            const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src + c * 8);
+            v.x = s16[0] | ((uint32_t)s16[1] << 16);
+            v.y = s16[2] | ((uint32_t)s16[3] << 16);
+            v.z = s16[4] | ((uint32_t)s16[5] << 16);
+            v.w = s16[6] | ((uint32_t)s16[7] << 16);
+          }
+        }
+        *reinterpret_cast<uint4*>(dst + c * 8) = v;
+      }
+    }
+    {
+      const bool live = o0 + r < n_out;
+      const __nv_bfloat16* src = wh + (int64_t)r * k + k0;
+      __nv_bfloat16* dst = Ws + r * kHmStride;
+      for (int c = tid & 1; c < cpr; c += 2)
+        *reinterpret_cast<uint4*>(dst + c * 8) = live ? __ldg(reinterpret_cast<const uint4*>(src + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    const __nv_bfloat16* ap = Xs + (warp * 16 + (lane & 15)) * kHmStride + (lane >> 4) * 8;
+    const __nv_bfloat16* bp = Ws + ((lane & 7) + (lane >> 4) * 8) * kHmStride + ((lane >> 3) & 1) * 8;
+    for (int kk = 0; kk < kc; kk += 16) {
+      uint32_t a[4];
+      ldsm_x4(a, ap + kk);
+#pragma unroll
+      for (int n2 = 0; n2 < 4; ++n2) {
+        uint32_t b[4];
+        ldsm_x4(b, bp + n2 * 16 * kHmStride + kk);
+        mma_bf16(acc[2 * n2][0], acc[2 * n2][1], acc[2 * n2][2], acc[2 * n2][3], a, b[0], b[1]);
+        mma_bf16(acc[2 * n2 + 1][0], acc[2 * n2 + 1][1], acc[2 * n2 + 1][2], acc[2 * n2 + 1][3], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int t = t0 + warp * 16 + (lane >> 2) + half * 8;
+    if (t >= T) continue;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int o = o0 + nt * 8 + (lane & 3) * 2 + e;
+        if (o >= n_out) continue;
+        float v = acc[nt][half * 2 + e];
+        if (gate) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(int64_t)t * ldg + (int64_t)h * g_hs + o])));
+        stx<YT>(y, (int64_t)t * ldy + (int64_t)h * y_hs + o, v);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 int latent_prep(bool f32, const void* qkv, int64_t ld, const float* norm_w, const int32_t* positions, const int32_t* slots,
@@ -136,6 +233,21 @@ static int head_linear_t(const void* x, int64_t ldx_, int x_hs, const __nv_bfloa
 int head_linear(bool f32, bool y_f32, const void* x, int64_t ldx_, int x_hs, const __nv_bfloat16* w, void* y, int64_t ldy, int y_hs,
                 const void* gate, int64_t ldg, int g_hs, int T, int heads, int n_out, int k, cudaStream_t s) {
   if (T == 0) return B200_OK;
+  static const int mma_env = getenv("B200_HEAD_LINEAR_MMA") ? atoi(getenv("B200_HEAD_LINEAR_MMA")) : 1;
+  if (!f32 && mma_env && k % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+    const bool vec = ldx_ % 8 == 0 && x_hs % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    const dim3 grid((T + kHmRows - 1) / kHmRows, heads, (n_out + kHmOuts - 1) / kHmOuts), block(128);
+#define HM(YT, VEC)                                                                                                               \
+  B200_CUDA(launch(head_linear_mma_kernel<YT, VEC>, grid, block, (size_t)0, s, (const __nv_bfloat16*)x, ldx_, x_hs, w, (YT*)y, ldy, y_hs, \
+                   (const __nv_bfloat16*)gate, ldg, g_hs, T, n_out, k))
+    if (y_f32) {
+      if (vec) HM(float, true); else HM(float, false);
+    } else {
+      if (vec) HM(__nv_bfloat16, true); else HM(__nv_bfloat16, false);
+    }
+#undef HM
+    return B200_OK;
+  }
   if (f32) return head_linear_t<float, float>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, T, heads, n_out, k, s);
   if (y_f32) return head_linear_t<__nv_bfloat16, float>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, T, heads, n_out, k, s);
   return head_linear_t<__nv_bfloat16, __nv_bfloat16>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, T, heads, n_out, k, s);

@@ -8,8 +8,8 @@
 //
 //  * mlstm_gates: the two gate projections with fp32 accumulation and the gate transforms, [T][2 heads] fp32;
 //  * mlstm_scan: the recurrence.  One CTA per (sequence, head, 32 value columns) walks the sequence's rows of the step in
-//    order (a decode row is a walk of one); a warp owns 4 columns, a lane the key dimensions lane, lane + 32, ...; the
-//    state lives in registers during the walk and is stored as [head][vdim][dim] so that a warp's loads are contiguous.
+//    order (a decode row is a walk of one), 16 rows staged in shared memory at a time; a warp owns 4 columns, a lane the
+//    key dimensions lane, lane + 32, ...; the state lives in registers during the walk and is stored as [head][vdim][dim] so that a warp's loads are contiguous.
 //    n and m are kept once per CTA (every CTA of a head needs them from the step before, so they cannot share one copy
 //    that one of them overwrites).  A sequence whose first row is at position 0 starts from zeros.
 //  * head_norm_gate: unit RMS per head, weight, sigmoid gate.
@@ -53,6 +53,7 @@ mlstm_gates_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict__ w
 constexpr int kScanCols = 4;                 // value columns per warp
 constexpr int kScanWarps = 8;
 constexpr int kScanBlockCols = kScanCols * kScanWarps;
+constexpr int kScanStage = 16;               // rows staged in shared memory at a time
 
 template <typename AT, int DPL>
 __global__ void __launch_bounds__(kScanWarps * 32)
@@ -81,59 +82,69 @@ mlstm_scan_kernel(const AT* __restrict__ qkv, int64_t ld, int q_off, int k_off, 
   }
   float m = fresh ? 0.f : *m_st;
   __syncthreads();   // every warp has read n and m before warp 0 may store them
-  float qn[DPL], kn[DPL], vn[kScanCols], ign, fgn;
-  auto fetch = [&](int t) {
-    const AT* row = qkv + (int64_t)t * ld;
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-      const int d = lane + 32 * i;
-      qn[i] = d < dim ? ldx<AT>(row, q_off + h * dim + d) * qscale : 0.f;
-      kn[i] = d < dim ? ldx<AT>(row, k_off + h * dim + d) : 0.f;
+  // The rows of the step are staged kScanStage at a time: q (scaled), k, this CTA's 32 value columns and the two gates of
+  // the head, loaded by the whole CTA with one round trip to memory per stage; the walk itself reads shared memory only.
+  extern __shared__ float stage[];
+  float* sq = stage;                          // [kScanStage][dim]
+  float* sk = sq + kScanStage * dim;          // [kScanStage][dim]
+  float* sv = sk + kScanStage * dim;          // [kScanStage][32]
+  float* sg = sv + kScanStage * kScanBlockCols;   // [kScanStage][2]
+  const int jb = zb * kScanBlockCols;
+  for (int b0 = 0; b0 < n_rows; b0 += kScanStage) {
+    const int nb = min(kScanStage, n_rows - b0);
+    __syncthreads();   // the stage before has been consumed
+    for (int e = threadIdx.x; e < nb * dim; e += kScanWarps * 32) {
+      const int r = e / dim, d = e % dim;
+      const AT* row = qkv + (int64_t)(start + b0 + r) * ld;
+      sq[e] = ldx<AT>(row, q_off + h * dim + d) * qscale;
+      sk[e] = ldx<AT>(row, k_off + h * dim + d);
     }
-#pragma unroll
-    for (int c = 0; c < kScanCols; ++c) vn[c] = j0 + c < vd ? ldx<AT>(row, v_off + h * vd + j0 + c) : 0.f;
-    ign = gates[(int64_t)t * 2 * heads + h];
-    fgn = gates[(int64_t)t * 2 * heads + heads + h];
-  };
-  fetch(start);
-  for (int r = 0; r < n_rows; ++r) {
-    const int t = start + r;
-    float q[DPL], k[DPL], v[kScanCols];
-    const float ig = ign, fg = fgn;
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-      q[i] = qn[i];
-      k[i] = kn[i];
+    for (int e = threadIdx.x; e < nb * kScanBlockCols; e += kScanWarps * 32) {
+      const int r = e / kScanBlockCols, j = jb + e % kScanBlockCols;
+      sv[e] = j < vd ? ldx<AT>(qkv + (int64_t)(start + b0 + r) * ld, v_off + h * vd + j) : 0.f;
     }
+    for (int e = threadIdx.x; e < nb * 2; e += kScanWarps * 32)
+      sg[e] = gates[(int64_t)(start + b0 + (e >> 1)) * 2 * heads + (e & 1) * heads + h];
+    __syncthreads();
+    for (int r = 0; r < nb; ++r) {
+      const int t = start + b0 + r;
+      float q[DPL], k[DPL], v[kScanCols];
+      const float ig = sg[2 * r], fg = sg[2 * r + 1];
 #pragma unroll
-    for (int c = 0; c < kScanCols; ++c) v[c] = vn[c];
-    if (r + 1 < n_rows) fetch(t + 1);
-    const float m_new = fmaxf(fg + m, ig);
-    const float a = expf(fg + m - m_new), b = expf(ig - m_new);
-    m = m_new;
-    float nq = 0.f, acc[kScanCols];
+      for (int i = 0; i < DPL; ++i) {
+        const int d = lane + 32 * i;
+        q[i] = d < dim ? sq[r * dim + d] : 0.f;
+        k[i] = d < dim ? sk[r * dim + d] : 0.f;
+      }
 #pragma unroll
-    for (int c = 0; c < kScanCols; ++c) acc[c] = 0.f;
+      for (int c = 0; c < kScanCols; ++c) v[c] = sv[r * kScanBlockCols + warp * kScanCols + c];
+      const float m_new = fmaxf(fg + m, ig);
+      const float a = expf(fg + m - m_new), b = expf(ig - m_new);
+      m = m_new;
+      float nq = 0.f, acc[kScanCols];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-      const float bk = b * k[i];
-      nr[i] = fmaf(a, nr[i], bk);
-      nq = fmaf(nr[i], q[i], nq);
+      for (int c = 0; c < kScanCols; ++c) acc[c] = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const float bk = b * k[i];
+        nr[i] = fmaf(a, nr[i], bk);
+        nq = fmaf(nr[i], q[i], nq);
+#pragma unroll
+        for (int c = 0; c < kScanCols; ++c) {
+          Sr[c][i] = fmaf(a, Sr[c][i], bk * v[c]);
+          acc[c] = fmaf(Sr[c][i], q[i], acc[c]);
+        }
+      }
+      nq = warp_sum(nq);
+      const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+      float mine = 0.f;
 #pragma unroll
       for (int c = 0; c < kScanCols; ++c) {
-        Sr[c][i] = fmaf(a, Sr[c][i], bk * v[c]);
-        acc[c] = fmaf(Sr[c][i], q[i], acc[c]);
+        const float o = warp_sum(acc[c]);
+        if (lane == c) mine = o;
       }
+      if (lane < kScanCols && j0 + lane < vd) out[((int64_t)t * heads + h) * vd + j0 + lane] = mine / den;
     }
-    nq = warp_sum(nq);
-    const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
-    float mine = 0.f;
-#pragma unroll
-    for (int c = 0; c < kScanCols; ++c) {
-      const float o = warp_sum(acc[c]);
-      if (lane == c) mine = o;
-    }
-    if (lane < kScanCols && j0 + lane < vd) out[((int64_t)t * heads + h) * vd + j0 + lane] = mine / den;
   }
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
@@ -207,8 +218,9 @@ static int mlstm_scan_t(const void* qkv, int64_t ld, int q_off, int k_off, int v
   const dim3 grid(S, heads, mlstm_col_blocks(vd)), block(kScanWarps * 32);
   const float qscale = 1.0f / sqrtf((float)dim);
   const int dpl = (dim + 31) / 32;
+  const size_t smem = (size_t)kScanStage * (2 * dim + kScanBlockCols + 2) * 4;   // <= 34 KiB for dim <= 256
 #define SCAN(D)                                                                                                                   \
-  B200_CUDA(launch(mlstm_scan_kernel<AT, D>, grid, block, (size_t)0, s, (const AT*)qkv, ld, q_off, k_off, v_off, gates, positions, \
+  B200_CUDA(launch(mlstm_scan_kernel<AT, D>, grid, block, smem, s, (const AT*)qkv, ld, q_off, k_off, v_off, gates, positions, \
                    seq_start, seq_slots, state, slot_stride, out, heads, dim, vd, qscale))
   if (dpl <= 1) SCAN(1);
   else if (dpl <= 2) SCAN(2);

@@ -226,13 +226,16 @@ def test_latent_attention_on_the_tensor_cores(heads, rank, rd, with_sink):
 
 
 @pytest.mark.parametrize("f32", [1, 0])
-@pytest.mark.parametrize("heads,dim,rd,rot_dims,rank,vdim,gate", [(3, 24, 16, 16, 40, 20, True), (2, 16, 24, 8, 28, 36, False), (5, 70, 2, 2, 9, 3, True)])
+@pytest.mark.parametrize("heads,dim,rd,rot_dims,rank,vdim,gate", [(3, 24, 16, 16, 40, 20, True), (2, 16, 24, 8, 28, 36, False), (5, 70, 2, 2, 9, 3, True),
+                                                                  (4, 32, 16, 16, 48, 40, True), (2, 144, 64, 64, 256, 72, False)])
 def test_latent_rows_rotation_and_the_per_head_expansions(f32, heads, dim, rd, rot_dims, rank, vdim, gate):
     g = torch.Generator().manual_seed(dim + rank)
     T, bs, eps, base = 11, 8, 1e-5, 3000.0
     adt = torch.float32 if f32 else torch.bfloat16
     qh, krow = dim + rd, rank + rd
-    ld = heads * qh + krow + (heads * vdim if gate else 0) + 3
+    # inner sizes that are multiples of 16 take the tensor-core form in bf16 mode (rows that allow 16-byte copies and rows that
+    # do not), everything else and the 32-bit mode the CUDA-core form
+    ld = heads * qh + krow + (heads * vdim if gate else 0) + (3 if dim != 32 else 0)
     qkv = torch.randn(T, ld, generator=g).to(adt).float()
     nw = U.bf16_exact(1 + 0.2 * torch.randn(rank, generator=g))
     pos = [0, 1, 2, 7, 8, 9, 63, 64, 100, 511, 300]
