@@ -142,23 +142,60 @@ constexpr int kRunRows = 16;
 constexpr int kTileKeys = 32;
 constexpr int kTcThreads = 256;
 
-__global__ void attn_runs_plan_kernel(const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ ctx_lens, int T,
-                                      int32_t* __restrict__ runs, int32_t* __restrict__ n_runs) {
+// One CTA of 1024 threads.  Row t opens a segment when it is the step's first row, belongs to another sequence than row
+// t - 1, or does not continue its context length by one; inside a segment a run starts every kRunRows rows.  Per chunk of
+// 1024 rows: an inclusive max-scan carries every row's segment start, a prefix sum of the run starts gives each run its place.
+__global__ void __launch_bounds__(1024)
+attn_runs_plan_kernel(const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ ctx_lens, int T, int32_t* __restrict__ runs,
+                      int32_t* __restrict__ n_runs) {
+  __shared__ int wseg[32], wcnt[32];
+  __shared__ int carry_seg, carry_cnt;
   pdl_wait();
   pdl_launch_dependents();
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  int n = 0, start = 0;
-  for (int t = 1; t <= T; ++t) {
-    const bool cont = t < T && t - start < kRunRows && (row_to_seq ? row_to_seq[t] == row_to_seq[t - 1] : false) &&
-                      ctx_lens[t] == ctx_lens[t - 1] + 1;
-    if (!cont) {
-      runs[2 * n] = start;
-      runs[2 * n + 1] = t - start;
-      ++n;
-      start = t;
-    }
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    carry_seg = 0;
+    carry_cnt = 0;
   }
-  *n_runs = n;
+  __syncthreads();
+  for (int c0 = 0; c0 < T; c0 += 1024) {
+    const int t = c0 + tid;
+    const bool live = t < T;
+    const bool brk = live && (t == 0 || row_to_seq == nullptr || row_to_seq[t] != row_to_seq[t - 1] || ctx_lens[t] != ctx_lens[t - 1] + 1);
+    int seg = brk ? t : -1;                       // latest segment start at or before t (within the warp, then the chunk)
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, seg, o);
+      if (lane >= o) seg = max(seg, v);
+    }
+    if (lane == 31) wseg[warp] = seg;
+    __syncthreads();
+    int before = carry_seg;
+    for (int w = 0; w < warp; ++w) before = max(before, wseg[w]);
+    seg = max(seg, before);
+    const bool starts = live && (t - seg) % kRunRows == 0;
+    int cnt = starts ? 1 : 0;                     // inclusive prefix count of run starts
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, cnt, o);
+      if (lane >= o) cnt += v;
+    }
+    if (lane == 31) wcnt[warp] = cnt;
+    __syncthreads();
+    int base = carry_cnt;
+    for (int w = 0; w < warp; ++w) base += wcnt[w];
+    if (starts) runs[2 * (base + cnt - 1)] = t;
+    __syncthreads();
+    if (tid == 1023) {
+      carry_seg = seg;
+      carry_cnt = base + cnt;
+    }
+    __syncthreads();
+  }
+  // lengths: a run ends where the next one starts
+  const int n = carry_cnt;
+  for (int i = tid; i < n; i += 1024) runs[2 * i + 1] = (i + 1 < n ? runs[2 * (i + 1)] : T) - runs[2 * i];
+  if (tid == 0) *n_runs = n;
 }
 
 template <typename CT, typename AT>
@@ -288,7 +325,7 @@ int64_t paged_attn_anydim_workspace_bytes(int T) { return ((int64_t)2 * T + 8) *
 int paged_attn_runs_plan(const int32_t* row_to_seq, const int32_t* ctx_lens, int T, void* ws, cudaStream_t s) {
   int32_t* runs = static_cast<int32_t*>(ws) + 8;
   int32_t* n_runs = static_cast<int32_t*>(ws);
-  B200_CUDA(launch(attn_runs_plan_kernel, dim3(1), dim3(32), (size_t)0, s, row_to_seq, ctx_lens, T, runs, n_runs));
+  B200_CUDA(launch(attn_runs_plan_kernel, dim3(1), dim3(1024), (size_t)0, s, row_to_seq, ctx_lens, T, runs, n_runs));
   return B200_OK;
 }
 
@@ -302,7 +339,7 @@ static int paged_attn_anydim_t(const float* q, const void* kc, const void* vc, c
   if (plan != 0 && ws != nullptr && kRunRows * G <= 16 * (kTcThreads / 32) && smem_runs <= 200 * 1024) {
     int32_t* runs = static_cast<int32_t*>(ws) + 8;
     int32_t* n_runs = static_cast<int32_t*>(ws);
-    if (plan == 1) B200_CUDA(launch(attn_runs_plan_kernel, dim3(1), dim3(32), 0, s, row_to_seq, ctx_lens, T, runs, n_runs));
+    if (plan == 1) B200_CUDA(launch(attn_runs_plan_kernel, dim3(1), dim3(1024), 0, s, row_to_seq, ctx_lens, T, runs, n_runs));
     static bool done[64] = {};
     if (smem_runs > 48 * 1024) B200_CUDA(ensure_dynamic_smem(paged_attn_runs_kernel<CT, AT>, 200 * 1024, done));
     B200_CUDA(launch(paged_attn_runs_kernel<CT, AT>, dim3(T, kv_heads), dim3(kTcThreads), smem_runs, s, q, (const CT*)kc,

@@ -6,7 +6,7 @@
 // the block table), S = Q K^T and O += P V run as bf16 mma.sync m16n8k16 with fp32 accumulators, and the softmax between
 // them is fp32: scores scaled and masked per pair (a pair sees keys below its own context length), running maximum and sum
 // per pair, weights rounded to bf16 only as the second product's operand.  An optional per-head sink joins the denominator
-// at the end.  Warp w owns keys 16w..16w+15 of a tile for the scores and value columns 16(w + 4g) .. for the output.
+// at the end.  Warp w (of 8) owns keys 8w..8w+7 of a tile for the scores and value columns 16(w + 8g) .. for the output.
 //
 // Queries come as fp32 rows [T][heads][krow] (rounded to bf16 when staged); output rows are bf16 [T][heads][rank].
 // Shapes: krow and rank multiples of 16, rank <= 512.  Everything else (and the 32-bit mode) takes attn_anydim.cu; both walk
@@ -20,13 +20,16 @@
 namespace b200 {
 namespace {
 
-constexpr int kLaKeys = 64, kLaPairs = 16, kLaThreads = 128;
+constexpr int kLaKeys = 64, kLaPairs = 16, kLaWarps = 8, kLaThreads = kLaWarps * 32;
 constexpr int kSsStride = kLaKeys + 4;    // fp32 score rows
 constexpr int kPsStride = kLaKeys + 8;    // bf16 weight rows (144 bytes: 16-byte aligned, conflict-free for ldmatrix)
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
 }
 __device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
@@ -41,7 +44,7 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <int NG>   // 16-column output groups per warp: rank <= 64 NG
+template <int NG>   // 16-column output groups per warp: rank <= 128 NG
 __global__ void __launch_bounds__(kLaThreads)
 latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const int32_t* __restrict__ block_table,
                        int bt_stride, const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ ctx_lens,
@@ -89,46 +92,43 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
   for (int base = 0; base < ctx_max; base += kLaKeys) {
     const int n = min(kLaKeys, ctx_max - base);
     {
-      // two threads per key row, alternate 16-byte chunks: one block-table lookup per thread and tile
-      const int r = tid >> 1;
+      // four threads per key row, alternate 16-byte chunks: one block-table lookup per thread and tile
+      const int r = tid >> 2;
       __nv_bfloat16* dst = Ks + r * ks;
       if (r < n) {
         const int j = base + r;
         const __nv_bfloat16* src = kc + ((int64_t)bt[j / block_size] * block_size + j % block_size) * krow;
-        for (int c = tid & 1; c < cpr; c += 2) cp_async16(dst + c * 8, src + c * 8);
+        for (int c = tid & 3; c < cpr; c += 4) cp_async16(dst + c * 8, src + c * 8);
       } else {
         // rows past the context: finite values under zero weights
-        for (int c = tid & 1; c < cpr; c += 2) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        for (int c = tid & 3; c < cpr; c += 4) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     cp_async_wait_all();
     __syncthreads();
-    // scores of this warp's 16 keys for all 16 pairs
+    // scores of this warp's 8 keys for all 16 pairs
     {
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       const __nv_bfloat16* ap = Qs + (lane & 15) * ks + (lane >> 4) * 8;
-      const __nv_bfloat16* bp = Ks + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * ks + ((lane >> 3) & 1) * 8;
+      const __nv_bfloat16* bp = Ks + (warp * 8 + (lane & 7)) * ks + ((lane >> 3) & 1) * 8;
+#pragma unroll 4
       for (int k0 = 0; k0 < krow; k0 += 16) {
-        uint32_t a[4], b[4];
+        uint32_t a[4], b[2];
         ldsm_x4(a, ap + k0);
-        ldsm_x4(b, bp + k0);
-        mma_bf16(s[0][0], s[0][1], s[0][2], s[0][3], a, b[0], b[1]);
-        mma_bf16(s[1][0], s[1][1], s[1][2], s[1][3], a, b[2], b[3]);
+        ldsm_x2(b, bp + k0);
+        mma_bf16(s0, s1, s2, s3, a, b[0], b[1]);
       }
-      const int row = lane >> 2, col = warp * 16 + (lane & 3) * 2;
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        Ss[row * kSsStride + col + nt * 8] = s[nt][0];
-        Ss[row * kSsStride + col + nt * 8 + 1] = s[nt][1];
-        Ss[(row + 8) * kSsStride + col + nt * 8] = s[nt][2];
-        Ss[(row + 8) * kSsStride + col + nt * 8 + 1] = s[nt][3];
-      }
+      const int row = lane >> 2, col = warp * 8 + (lane & 3) * 2;
+      Ss[row * kSsStride + col] = s0;
+      Ss[row * kSsStride + col + 1] = s1;
+      Ss[(row + 8) * kSsStride + col] = s2;
+      Ss[(row + 8) * kSsStride + col + 1] = s3;
     }
     __syncthreads();
-    // softmax bookkeeping: this warp's 4 pairs, two keys per lane
+    // softmax bookkeeping: this warp's 2 pairs, two keys per lane
 #pragma unroll
-    for (int rr = 0; rr < 4; ++rr) {
-      const int row = warp * 4 + rr, c = ctxp[row];
+    for (int rr = 0; rr < kLaPairs / kLaWarps; ++rr) {
+      const int row = warp * (kLaPairs / kLaWarps) + rr, c = ctxp[row];
       const int j0 = base + lane, j1 = j0 + 32;
       const float s0 = j0 < c ? Ss[row * kSsStride + lane] * scale : -INFINITY;
       const float s1 = j1 < c ? Ss[row * kSsStride + lane + 32] * scale : -INFINITY;
@@ -167,7 +167,7 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
         ldsm_x4(a, ap + kk * 16);
 #pragma unroll
         for (int g = 0; g < NG; ++g) {
-          const int col0 = (warp + 4 * g) * 16;
+          const int col0 = (warp + kLaWarps * g) * 16;
           if (col0 < rank) {
             uint32_t b[4];
             ldsm_x4_t(b, vp + kk * 16 * ks + col0);
@@ -195,7 +195,7 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     __nv_bfloat16* dst = out + ((int64_t)t * heads + h) * rank;
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
-      const int col0 = (warp + 4 * g) * 16;
+      const int col0 = (warp + kLaWarps * g) * 16;
       if (col0 < rank) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
@@ -232,10 +232,9 @@ int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* bloc
     B200_CUDA(launch(latent_attn_mma_kernel<NGV>, grid, block, smem, s, q, kc, block_table, bt_stride, row_to_seq, ctx_lens, out, runs, \
                      n_runs, heads, krow, rank, block_size, scale, sink));                                                          \
   } while (0)
-  if (rank <= 64) LA(1);
-  else if (rank <= 128) LA(2);
-  else if (rank <= 256) LA(4);
-  else LA(8);
+  if (rank <= 128) LA(1);
+  else if (rank <= 256) LA(2);
+  else LA(4);
 #undef LA
   return B200_OK;
 }

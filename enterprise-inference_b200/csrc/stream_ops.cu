@@ -246,7 +246,7 @@ logit_cap_kernel(const float* __restrict__ in, float* __restrict__ out_f32, __nv
   pdl_wait();
   pdl_launch_dependents();
   const int64_t r = blockIdx.x;
-  for (int c = threadIdx.x; c < ld; c += 256) {
+  for (int c = blockIdx.y * 256 + threadIdx.x; c < ld; c += gridDim.y * 256) {
     float v = 0.f;
     if (c < vocab) {
       v = in[r * vocab + c];
@@ -348,7 +348,7 @@ int ff_act(bool f32, const void* in, void* out, int T, int ff, bool gated, int k
 
 int logit_cap(const float* in, float* out_f32, __nv_bfloat16* out_bf16, int R, int vocab, int ld, float cap, cudaStream_t s) {
   if (R == 0) return B200_OK;
-  B200_CUDA(launch(logit_cap_kernel, dim3(R), dim3(256), (size_t)0, s, in, out_f32, out_bf16, vocab, ld, cap));
+  B200_CUDA(launch(logit_cap_kernel, dim3(R, std::max(1, std::min(ld / 1024, 64))), dim3(256), (size_t)0, s, in, out_f32, out_bf16, vocab, ld, cap));
   return B200_OK;
 }
 
