@@ -351,7 +351,7 @@ int mlstm_col_blocks(int vd);
 int64_t mlstm_state_floats(int heads, int dim, int vd);
 int mlstm_scan(bool f32, const void* qkv, int64_t ld, int q_off, int k_off, int v_off, const float* gates, const int32_t* positions,
                const int32_t* seq_start, const int32_t* seq_slots, float* state, int64_t slot_stride, float* out, int S, int heads,
-               int dim, int vd, cudaStream_t s);
+               int dim, int vd, cudaStream_t s, bool single_rows = false);   // single_rows: every sequence of the step has one row
 int head_norm_gate(bool f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int T, int heads, int vd, float eps,
                    cudaStream_t s);
 // true-fp32 CUDA-core linear (linear_simt.cu)

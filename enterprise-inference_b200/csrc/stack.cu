@@ -260,7 +260,7 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
       const int hd = L.heads * L.dim;
       STEP(mlstm_gates(f32, M->hc, W.gates, W.gates_bias, M->gates_buf, T, Wd, L.heads, L.gate_cap, s));
       STEP(mlstm_scan(f32, M->qkv, qr, 0, hd, 2 * hd, M->gates_buf, a.positions, M->seq_start, seq_slots, M->state + W.rec_off,
-                      M->slot_floats, M->oraw, S, L.heads, L.dim, L.vdim, s));
+                      M->slot_floats, M->oraw, S, L.heads, L.dim, L.vdim, s, S == T));
       const char* gptr = static_cast<const char*>(M->qkv) + (int64_t)(2 * hd + av) * es;
       STEP(head_norm_gate(f32, M->oraw, W.head_norm, gptr, qr, M->attn, T, L.heads, L.vdim, m.norm_eps, s));
     }

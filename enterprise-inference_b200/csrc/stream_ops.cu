@@ -105,18 +105,18 @@ __global__ void prev_token_commit_kernel(const int32_t* __restrict__ ids, int vo
 // u = sum_j dwa[j] * results[j] over the n_results earlier results (result n_results - 1 being X_new); else u = X_new;
 // (3) with g1: unit = u / sqrt(mean(u^2) + eps); h1 = unit * g1[0] (fp32 and / or activation type), h2 = unit * g2[0].
 template <typename AT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 parallel_close_kernel(float* __restrict__ u, const AT* __restrict__ y_mix, const AT* __restrict__ y_ff, const float* __restrict__ parts,
                       int n_parts, const AT* __restrict__ y_sh, float* __restrict__ results, int64_t result_stride, int n_results,
                       const float* __restrict__ dwa, const float* __restrict__ g1, const float* __restrict__ g2,
                       float* __restrict__ h1_f32, AT* __restrict__ h1_act, AT* __restrict__ h2, int width, float eps) {
   extern __shared__ float row[];
-  __shared__ float red[8];
+  __shared__ float red[32];
   pdl_wait();
   pdl_launch_dependents();
   const int64_t t = blockIdx.x, o = t * width;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < width; c += 256) {
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float v = u[o + c];
     if (y_mix != nullptr) {
       float a = ldx<AT>(y_mix, o + c);
@@ -139,7 +139,7 @@ parallel_close_kernel(float* __restrict__ u, const AT* __restrict__ y_mix, const
   ss = block_sum_f(ss, red);
   const float inv = rsqrtf(ss / (float)width + eps);
   const float a1 = g1[0], a2 = g2 ? g2[0] : 0.f;
-  for (int c = threadIdx.x; c < width; c += 256) {
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float n = row[c] * inv;
     if (h1_f32) h1_f32[o + c] = n * a1;
     if (h1_act) stx<AT>(h1_act, o + c, n * a1);
@@ -164,7 +164,7 @@ canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* 
   const int hist = taps - 1;
   const int start = hist ? seq_start[s] : t, n = hist ? seq_start[s + 1] - start : 1, r = t - start;
   if (r >= hist) {
-    for (int c = threadIdx.x; c < width; c += 256) {
+    for (int c = blockIdx.y * 256 + threadIdx.x; c < width; c += gridDim.y * 256) {
       float a = h[(int64_t)t * width + c];
       float acc = 0.f;
       for (int j = 0; j < taps; ++j) acc = fmaf(w[c * taps + j], h[(int64_t)(t - hist + j) * width + c], acc);
@@ -175,7 +175,7 @@ canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* 
   if (r != 0) return;
   const int p0 = positions[t];
   float* tail = tails + (int64_t)seq_slots[s] * slot_stride;   // [hist][width]: inputs at positions p0 - hist .. p0 - 1
-  for (int c = threadIdx.x; c < width; c += 256) {
+  for (int c = blockIdx.y * 256 + threadIdx.x; c < width; c += gridDim.y * 256) {
     float old[kMaxTaps], wv[kMaxTaps];
 #pragma unroll
     for (int i = 0; i < kMaxTaps; ++i) {
@@ -290,14 +290,16 @@ int parallel_close(bool f32, float* u, const void* y_mix, const void* y_ff, cons
   const size_t smem = (size_t)width * 4;
   B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "parallel_close: width %d does not fit shared memory", width);
   static bool done[2][64] = {};
+  // steps of few rows: few elements per thread, so that a row's loads are in flight together; long steps fill the SMs anyway
+  const int threads = T >= 512 ? 256 : (width >= 2048 ? 1024 : (width >= 1024 ? 512 : 256));
   if (f32) {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(parallel_close_kernel<float>, 200 * 1024, done[0]));
-    B200_CUDA(launch(parallel_close_kernel<float>, dim3(T), dim3(256), smem, s, u, (const float*)y_mix, (const float*)y_ff, parts,
+    B200_CUDA(launch(parallel_close_kernel<float>, dim3(T), dim3(threads), smem, s, u, (const float*)y_mix, (const float*)y_ff, parts,
                      n_parts, (const float*)y_sh, results, result_stride, n_results, dwa, g1, g2, h1_f32, (float*)h1_act, (float*)h2,
                      width, eps));
   } else {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(parallel_close_kernel<__nv_bfloat16>, 200 * 1024, done[1]));
-    B200_CUDA(launch(parallel_close_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, s, u, (const __nv_bfloat16*)y_mix,
+    B200_CUDA(launch(parallel_close_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, s, u, (const __nv_bfloat16*)y_mix,
                      (const __nv_bfloat16*)y_ff, parts, n_parts, (const __nv_bfloat16*)y_sh, results, result_stride, n_results, dwa,
                      g1, g2, h1_f32, (__nv_bfloat16*)h1_act, (__nv_bfloat16*)h2, width, eps));
   }
@@ -311,10 +313,10 @@ int canon_conv(bool f32, const float* h, const float* w, void* out, int T, int w
   B200_REQUIRE(taps >= 1 && taps <= kMaxTaps, B200_ERR_UNSUPPORTED, "canon_conv: %d taps outside [1, %d]", taps, kMaxTaps);
   B200_REQUIRE(taps == 1 || (positions && seq_start && seq_slots && tails), B200_ERR_INVALID, "canon_conv: null argument");
   if (f32)
-    B200_CUDA(launch(canon_conv_kernel<float>, dim3(T), dim3(256), (size_t)0, s, h, w, (float*)out, width, taps, positions, row_to_seq,
+    B200_CUDA(launch(canon_conv_kernel<float>, dim3(T, (width + 255) / 256), dim3(256), (size_t)0, s, h, w, (float*)out, width, taps, positions, row_to_seq,
                      seq_start, seq_slots, tails, slot_stride));
   else
-    B200_CUDA(launch(canon_conv_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t)0, s, h, w, (__nv_bfloat16*)out, width, taps,
+    B200_CUDA(launch(canon_conv_kernel<__nv_bfloat16>, dim3(T, (width + 255) / 256), dim3(256), (size_t)0, s, h, w, (__nv_bfloat16*)out, width, taps,
                      positions, row_to_seq, seq_start, seq_slots, tails, slot_stride));
   return B200_OK;
 }
