@@ -141,7 +141,7 @@ SIGNATURES = {
     "b200_paged_attn_anydim_ex": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f32,
                                             _i32, _vp, _i32, _i32, _vp, _vp]),
     "b200_latent_attn_supported": (C.c_int, [_i32, _i32, _i32]),
-    "b200_latent_attn": (C.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp]),
+    "b200_latent_attn": (C.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i32, _vp, _vp]),
     "b200_mlstm_gates": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
     "b200_mlstm_state_floats": (_i64, [_i32, _i32, _i32]),
     "b200_mlstm_scan": (C.c_int, [_i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _vp]),

@@ -8,6 +8,9 @@
 // per pair, weights rounded to bf16 only as the second product's operand.  An optional per-head sink joins the denominator
 // at the end.  Warp w (of 8) owns keys 8w..8w+7 of a tile for the scores and value columns 16(w + 8g) .. for the output.
 //
+// Steps with few (row, head) pairs and long contexts split the context over several CTAs per pair group (n_splits): each
+// leaves unnormalised sums with its maximum and denominator, a merge kernel combines them.
+//
 // Queries come as fp32 rows [T][heads][krow] (rounded to bf16 when staged); output rows are bf16 [T][heads][rank].
 // Shapes: krow and rank multiples of 16, rank <= 512.  Everything else (and the 32-bit mode) takes attn_anydim.cu; both walk
 // the same cache and the same run list, and agree within bf16 rounding of the operands.
@@ -49,7 +52,8 @@ __global__ void __launch_bounds__(kLaThreads)
 latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const int32_t* __restrict__ block_table,
                        int bt_stride, const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ ctx_lens,
                        __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ runs, const int32_t* __restrict__ n_runs, int heads,
-                       int krow, int rank, int block_size, float scale, const float* __restrict__ sink) {
+                       int krow, int rank, int block_size, float scale, const float* __restrict__ sink, int n_splits,
+                       float* __restrict__ part) {
   extern __shared__ __align__(16) unsigned char smraw[];
   pdl_wait();
   pdl_launch_dependents();
@@ -74,9 +78,11 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     mrow[tid] = -INFINITY;
     lrow[tid] = 0.f;
   }
-  for (int e = tid; e < kLaPairs * krow; e += kLaThreads) {
-    const int p = e / krow, d = e % krow, i = i0 + p;
-    Qs[p * ks + d] = __float2bfloat16_rn(i < nq ? q[((int64_t)(t0 + i / heads) * heads + i % heads) * krow + d] : 0.f);
+#pragma unroll 4
+  for (int p = 0; p < kLaPairs; ++p) {
+    const int i = i0 + p;
+    const float* src = q + ((int64_t)(t0 + i / heads) * heads + i % heads) * krow;
+    for (int d = tid; d < krow; d += kLaThreads) Qs[p * ks + d] = __float2bfloat16_rn(i < nq ? src[d] : 0.f);
   }
   const int last_row = min(nr - 1, (i0 + kLaPairs - 1) / heads);
   const int ctx_max = ctx_lens[t0 + last_row];
@@ -89,7 +95,10 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     for (int j = 0; j < 8; ++j) o[g][j] = 0.f;
   __syncthreads();
 
-  for (int base = 0; base < ctx_max; base += kLaKeys) {
+  // with n_splits > 1 this CTA walks only its share of the tiles and leaves unnormalised sums for the merge kernel
+  const int tiles = (ctx_max + kLaKeys - 1) / kLaKeys, per = (tiles + n_splits - 1) / n_splits;
+  const int base_lo = blockIdx.z * per * kLaKeys, base_hi = min(ctx_max, (int)(blockIdx.z + 1) * per * kLaKeys);
+  for (int base = base_lo; base < base_hi; base += kLaKeys) {
     const int n = min(kLaKeys, ctx_max - base);
     {
       // four threads per key row, alternate 16-byte chunks: one block-table lookup per thread and tile
@@ -179,6 +188,35 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     }
     __syncthreads();
   }
+  if (n_splits > 1) {
+    // partial rows [pair][split][rank | m | l] fp32
+    const int prow = rank + 2;
+    if (tid < kLaPairs && i0 + tid < nq) {
+      const int i = i0 + tid;
+      float* dst = part + (((int64_t)(t0 + i / heads) * heads + i % heads) * n_splits + blockIdx.z) * prow;
+      dst[rank] = mrow[tid];
+      dst[rank + 1] = lrow[tid];
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int p = (lane >> 2) + half * 8, i = i0 + p;
+      if (i >= nq) continue;
+      float* dst = part + (((int64_t)(t0 + i / heads) * heads + i % heads) * n_splits + blockIdx.z) * prow;
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        const int col0 = (warp + kLaWarps * g) * 16;
+        if (col0 < rank) {
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const int col = col0 + nt * 8 + (lane & 3) * 2;
+            dst[col] = o[g][nt * 4 + half * 2];
+            dst[col + 1] = o[g][nt * 4 + half * 2 + 1];
+          }
+        }
+      }
+    }
+    return;
+  }
   // finish: sink, normalise, store
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
@@ -208,7 +246,53 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
   }
 }
 
+// One warp per (row, head): the splits' sums are brought to one maximum (the sink's included), added and normalised.
+// Lane z holds split z's maximum and denominator; the per-split factors are then shared by shuffles and every lane's loads
+// of a column are independent of one another.
+constexpr int kLaMaxSplits = 16;
+__global__ void __launch_bounds__(128)
+latent_attn_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int n_pairs, int heads, int rank, int n_splits,
+                         const float* __restrict__ sink) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int pair = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (pair >= n_pairs) return;
+  const int prow = rank + 2;
+  const float* src = part + (int64_t)pair * n_splits * prow;
+  const float mz = lane < n_splits ? src[lane * prow + rank] : -INFINITY;
+  const float lz = lane < n_splits ? src[lane * prow + rank + 1] : 0.f;
+  const float sk = sink ? sink[pair % heads] : -INFINITY;
+  const float m = fmaxf(warp_max(mz), sk);
+  const float ez = mz != -INFINITY ? expf(mz - m) : 0.f;
+  const float l = warp_sum(lz * ez) + (sink ? expf(sk - m) : 0.f);
+  const float fz = l > 0.f ? ez / l : 0.f;
+  float f[kLaMaxSplits];
+#pragma unroll
+  for (int z = 0; z < kLaMaxSplits; ++z) f[z] = __shfl_sync(0xffffffffu, fz, z);
+  for (int c = lane; c < rank; c += 32) {
+    float v[kLaMaxSplits];
+#pragma unroll
+    for (int z = 0; z < kLaMaxSplits; ++z) v[z] = z < n_splits ? src[z * prow + c] : 0.f;
+    float a = 0.f;
+#pragma unroll
+    for (int z = 0; z < kLaMaxSplits; ++z) a = fmaf(v[z], f[z], a);
+    out[(int64_t)pair * rank + c] = __float2bfloat16_rn(a);
+  }
+}
+
 }  // namespace
+
+// Splits of the context for a step of T rows whose longest context is max_ctx: 1 when the (row, head) pairs fill the SMs
+// anyway; else enough CTAs for two per SM, at least two tiles each, within a workspace of ws_bytes.
+int latent_attn_splits(int T, int heads, int rank, int max_ctx, int64_t ws_bytes) {
+  const int ctas = (T * heads + kLaPairs - 1) / kLaPairs;
+  if (ctas >= kNumSMs || max_ctx < 4 * kLaKeys) return 1;
+  const int tiles = (max_ctx + kLaKeys - 1) / kLaKeys;
+  int n = std::min(std::min((tiles + 1) / 2, (2 * kNumSMs + ctas - 1) / ctas), kLaMaxSplits);
+  const int64_t per_split = (int64_t)T * heads * (rank + 2) * 4;
+  while (n > 1 && n * per_split > ws_bytes) --n;
+  return std::max(n, 1);
+}
 
 bool latent_attn_mma_supported(int heads, int krow, int rank) {
   static const int env = getenv("B200_LATENT_MMA") ? atoi(getenv("B200_LATENT_MMA")) : 1;
@@ -219,23 +303,28 @@ bool latent_attn_mma_supported(int heads, int krow, int rank) {
 // runs / n_runs: the run list of the step (attn_anydim.cu builds it: runs of at most 16 consecutive rows of one sequence)
 int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* block_table, int bt_stride, const int32_t* row_to_seq,
                     const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
-                    int rank, int block_size, float scale, const float* sink, cudaStream_t s) {
+                    int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits, float* part) {
   if (T == 0) return B200_OK;
+  if (n_splits < 1 || part == nullptr) n_splits = 1;
+  B200_REQUIRE(n_splits <= kLaMaxSplits, B200_ERR_INVALID, "latent_attn_mma: %d splits (at most %d)", n_splits, kLaMaxSplits);
   B200_REQUIRE(latent_attn_mma_supported(heads, krow, rank), B200_ERR_UNSUPPORTED, "latent_attn_mma: shape %d / %d / %d", heads, krow, rank);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(kc) % 16 == 0, B200_ERR_INVALID, "latent_attn_mma: cache not 16-byte aligned");
   const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 16);
-  const dim3 grid(T, (16 * heads + kLaPairs - 1) / kLaPairs), block(kLaThreads);
+  const dim3 grid(T, (16 * heads + kLaPairs - 1) / kLaPairs, n_splits), block(kLaThreads);
 #define LA(NGV)                                                                                                                     \
   do {                                                                                                                              \
     static bool done[64] = {};                                                                                                      \
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(latent_attn_mma_kernel<NGV>, 200 * 1024, done));                            \
     B200_CUDA(launch(latent_attn_mma_kernel<NGV>, grid, block, smem, s, q, kc, block_table, bt_stride, row_to_seq, ctx_lens, out, runs, \
-                     n_runs, heads, krow, rank, block_size, scale, sink));                                                          \
+                     n_runs, heads, krow, rank, block_size, scale, sink, n_splits, part));                                          \
   } while (0)
   if (rank <= 128) LA(1);
   else if (rank <= 256) LA(2);
   else LA(4);
 #undef LA
+  if (n_splits > 1)
+    B200_CUDA(launch(latent_attn_merge_kernel, dim3((T * heads + 3) / 4), dim3(128), (size_t)0, s, (const float*)part, out, T * heads, heads,
+                     rank, n_splits, sink));
   return B200_OK;
 }
 

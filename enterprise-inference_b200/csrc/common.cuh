@@ -304,7 +304,9 @@ int paged_attn_runs_plan(const int32_t* row_to_seq, const int32_t* ctx_lens, int
 bool latent_attn_mma_supported(int heads, int krow, int rank);
 int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* block_table, int bt_stride, const int32_t* row_to_seq,
                     const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
-                    int rank, int block_size, float scale, const float* sink, cudaStream_t s);
+                    int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits = 1, float* part = nullptr);
+// context splits for a step (1: none); part holds T * heads * n_splits * (rank + 2) floats
+int latent_attn_splits(int T, int heads, int rank, int max_ctx, int64_t ws_bytes);
 // mixture of experts (moe.cu)
 int64_t moe_workspace_bytes(int T, int top, int experts, int width, int ff);
 bool moe_tc_supported(int width, int ff);

@@ -72,6 +72,8 @@ struct StackModel {
   float *results = nullptr, *h1f = nullptr, *gates_buf = nullptr, *oraw = nullptr, *head_f32 = nullptr;
   void *hc = nullptr, *lat = nullptr, *y2 = nullptr, *y3 = nullptr, *gu = nullptr, *ffa = nullptr;
   int32_t* seq_start = nullptr;
+  float* lat_ws = nullptr;             // partial sums of the latent attention when a step's context is split over CTAs
+  int64_t lat_ws_bytes = 0;
 };
 
 bool paged_attn_tc_supported(int hq, int hkv, int block_size);   // attn_tc.cu
@@ -245,7 +247,8 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
         if (attn_plan == 1) attn_plan = 2;
         STEP(latent_attn_mma(M->q, (const __nv_bfloat16*)W.kc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens,
                              (__nv_bfloat16*)M->lat, static_cast<const int32_t*>(M->attn_ws) + 8, static_cast<const int32_t*>(M->attn_ws), T,
-                             L.heads, krow, L.kv_rank, m.block_size, L.scale, sink, s));
+                             L.heads, krow, L.kv_rank, m.block_size, L.scale, sink, s,
+                             latent_attn_splits(T, L.heads, L.kv_rank, a.max_ctx, M->lat_ws_bytes), M->lat_ws));
       } else {
         STEP(paged_attn_anydim(f32, M->q, W.kc, W.kc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
                                M->lat, T, L.heads, 1, krow, L.kv_rank, m.block_size, L.scale, runs_built && attn_plan == 1 ? 2 : attn_plan,
@@ -573,6 +576,12 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     M->attn_tc_ws_bytes = std::max(M->attn_tc_ws_bytes, paged_attn_workspace_bytes((int)T, tc_heads, max_ctx, cfg->block_size));
   }
 
+  M->lat_ws_bytes = 16;
+  if (par && !cfg->f32)
+    for (int l = 0; l < cfg->n_layers; ++l)
+      if (is_latent(layers[l]) && latent_attn_mma_supported(layers[l].heads, layers[l].kv_rank + layers[l].rot_dim, layers[l].kv_rank))
+        // splitting only happens below one CTA per SM: at most 148 * 16 pairs, 16 splits
+        M->lat_ws_bytes = std::max<int64_t>(M->lat_ws_bytes, std::min<int64_t>(T * layers[l].heads, 148 * 16) * 16 * (layers[l].kv_rank + 2) * 4);
   struct Item {
     void** p;
     int64_t bytes;
@@ -607,6 +616,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&M->oraw, max_gates ? T * max_a * 4 : 16},
       {(void**)&M->head_f32, par ? R * (int64_t)cfg->vocab * 4 : 16},
       {(void**)&M->seq_start, (T + 2) * 4},
+      {(void**)&M->lat_ws, M->lat_ws_bytes},
       {(void**)&c->lin_ws, c->lin_ws_bytes},
       {(void**)&c->d_meta, c->meta_ints * 4},
       {(void**)&c->d_tokens, R * 4},
@@ -999,11 +1009,12 @@ extern "C" int b200_latent_attn_supported(int32_t heads, int32_t k_row, int32_t 
 
 extern "C" int b200_latent_attn(const float* q, const void* cache, const int32_t* block_table, int32_t bt_stride, const int32_t* row_to_seq,
                                 const int32_t* ctx_lens, void* out, int32_t T, int32_t heads, int32_t k_row, int32_t rank,
-                                int32_t block_size, float scale, const float* sink, void* workspace, void* stream) {
+                                int32_t block_size, float scale, const float* sink, void* workspace, int32_t n_splits, float* part,
+                                void* stream) {
   B200_REQUIRE(q && cache && block_table && ctx_lens && out && workspace && block_size > 0, B200_ERR_INVALID, "latent_attn: bad argument");
   int rc = paged_attn_runs_plan(row_to_seq, ctx_lens, T, workspace, (cudaStream_t)stream);
   if (rc) return rc;
   return latent_attn_mma(q, (const __nv_bfloat16*)cache, block_table, bt_stride, row_to_seq, ctx_lens, (__nv_bfloat16*)out,
                          static_cast<const int32_t*>(workspace) + 8, static_cast<const int32_t*>(workspace), T, heads, k_row, rank,
-                         block_size, scale, sink, (cudaStream_t)stream);
+                         block_size, scale, sink, (cudaStream_t)stream, n_splits, part);
 }

@@ -567,11 +567,13 @@ B200_API int b200_paged_attn_anydim_ex(int32_t f32, const float* q, const void* 
                                        const float* sink, void* stream);
 /* The same attention over bf16 latent cache rows [block][block_size][k_row] on the tensor cores: one kv head, the value of a key
  * is the row's leading `rank` entries, fp32 queries [T][heads][k_row], bf16 output [T][heads][rank].  k_row and rank multiples
- * of 16, rank <= 512 (b200_latent_attn_supported).  workspace: b200_paged_attn_anydim_workspace_bytes(T). */
+ * of 16, rank <= 512 (b200_latent_attn_supported).  workspace: b200_paged_attn_anydim_workspace_bytes(T).  n_splits > 1 with
+ * part (n_tokens * heads * n_splits * (rank + 2) floats): the context is walked by n_splits CTAs per group of pairs and merged. */
 B200_API int b200_latent_attn_supported(int32_t heads, int32_t k_row, int32_t rank);
 B200_API int b200_latent_attn(const float* q, const void* cache, const int32_t* block_table, int32_t bt_stride, const int32_t* row_to_seq,
                               const int32_t* ctx_lens, void* out, int32_t n_tokens, int32_t heads, int32_t k_row, int32_t rank,
-                              int32_t block_size, float scale, const float* sink, void* workspace, void* stream);
+                              int32_t block_size, float scale, const float* sink, void* workspace, int32_t n_splits, float* part,
+                              void* stream);
 /* mLSTM: log gates [T][2 heads] (input gates, then forget gates) from w [2 heads][width] and bias; the recurrence over
  * fused rows (q at q_off, k at k_off, v at v_off) with the state of each sequence at state + slot * slot_stride floats
  * (b200_mlstm_state_floats per layer), out fp32 [T][heads*vdim]; then unit RMS per head, weight and sigmoid gate. */

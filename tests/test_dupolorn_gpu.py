@@ -191,10 +191,12 @@ def test_attention_over_latent_rows_sink_far_keys_and_block_borders(f32, heads, 
     assert torch.allclose(out.float().cpu().double(), want, atol=2e-5 if f32 else 2e-2, rtol=0 if f32 else 2e-2)
 
 
+@pytest.mark.parametrize("splits", [1, 3, 16])
 @pytest.mark.parametrize("heads,rank,rd,with_sink", [(3, 32, 16, True), (6, 128, 32, False), (16, 512, 64, True), (20, 64, 0, True), (1, 16, 16, False)])
-def test_latent_attention_on_the_tensor_cores(heads, rank, rd, with_sink):
+def test_latent_attention_on_the_tensor_cores(heads, rank, rd, with_sink, splits):
     """Decode rows and runs of consecutive rows (pairs of one CTA with different context lengths; more heads than a CTA holds
-    pairs), contexts around tile (64) and block borders, a key far back that decides two rows, the sink."""
+    pairs), contexts around tile (64) and block borders, a key far back that decides two rows, the sink; the context walked by
+    one CTA or split over several (more splits than short contexts have tiles: empty shares) and merged."""
     g = torch.Generator().manual_seed(rank + heads)
     bs, n_tok, scale, krow = 16, 600, 0.25, rank + rd
     assert lib().b200_latent_attn_supported(heads, krow, rank) == 1 and lib().b200_latent_attn_supported(heads, krow + 8, rank) == 0
@@ -217,9 +219,10 @@ def test_latent_attention_on_the_tensor_cores(heads, rank, rd, with_sink):
     ws = torch.zeros(int(lib().b200_paged_attn_anydim_workspace_bytes(T)), dtype=torch.uint8, device=DEV)
     bt = perm.to(torch.int32)[None, :].repeat(16, 1).contiguous()
     out = torch.full((T, heads, rank), float("nan"), dtype=torch.bfloat16, device=DEV)
+    part = torch.full((T * heads * splits * (rank + 2),), float("nan"), device=DEV)
     check(lib().b200_latent_attn(dev(q).data_ptr(), dev(kc).data_ptr(), dev(bt).data_ptr(), nb, i32(seq).data_ptr(), i32(ctxs).data_ptr(),
                                  out.data_ptr(), T, heads, krow, rank, bs, scale, dev(sink).data_ptr() if with_sink else None, ws.data_ptr(),
-                                 None))
+                                 splits, part.data_ptr() if splits > 1 else None, None))
     sync()
     assert torch.isfinite(out.float()).all()
     assert torch.allclose(out.float().cpu().double(), want, atol=2e-2, rtol=2e-2)
