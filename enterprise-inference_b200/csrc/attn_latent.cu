@@ -78,11 +78,9 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     mrow[tid] = -INFINITY;
     lrow[tid] = 0.f;
   }
-#pragma unroll 4
-  for (int p = 0; p < kLaPairs; ++p) {
-    const int i = i0 + p;
-    const float* src = q + ((int64_t)(t0 + i / heads) * heads + i % heads) * krow;
-    for (int d = tid; d < krow; d += kLaThreads) Qs[p * ks + d] = __float2bfloat16_rn(i < nq ? src[d] : 0.f);
+  for (int e = tid; e < kLaPairs * krow; e += kLaThreads) {
+    const int p = e / krow, d = e % krow, i = i0 + p;
+    Qs[p * ks + d] = __float2bfloat16_rn(i < nq ? q[((int64_t)(t0 + i / heads) * heads + i % heads) * krow + d] : 0.f);
   }
   const int last_row = min(nr - 1, (i0 + kLaPairs - 1) / heads);
   const int ctx_max = ctx_lens[t0 + last_row];
@@ -283,10 +281,11 @@ latent_attn_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restri
 }  // namespace
 
 // Splits of the context for a step of T rows whose longest context is max_ctx: 1 when the (row, head) pairs fill the SMs
-// anyway; else enough CTAs for two per SM, at least two tiles each, within a workspace of ws_bytes.
+// anyway or the context is short; else enough CTAs for two per SM, at least two tiles each, within a workspace of ws_bytes.
 int latent_attn_splits(int T, int heads, int rank, int max_ctx, int64_t ws_bytes) {
   const int ctas = (T * heads + kLaPairs - 1) / kLaPairs;
-  if (ctas >= kNumSMs || max_ctx < 4 * kLaKeys) return 1;
+  // measured at 513 tokens: with 64 pair groups the merge launch costs what the split saves, with one it pays
+  if (ctas >= kNumSMs || max_ctx <= (ctas < 16 ? 4 : 16) * kLaKeys) return 1;
   const int tiles = (max_ctx + kLaKeys - 1) / kLaKeys;
   int n = std::min(std::min((tiles + 1) / 2, (2 * kNumSMs + ctas - 1) / ctas), kLaMaxSplits);
   const int64_t per_split = (int64_t)T * heads * (rank + 2) * 4;
