@@ -432,7 +432,7 @@ def test_one_layer_models_and_their_streams_fp32(which):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("variant", ["odd sizes", "one tap, no shared expert, uncapped"])
+@pytest.mark.parametrize("variant", ["odd sizes", "one tap, no shared expert, uncapped", "no rotated part, every expert chosen"])
 def test_other_sizes_and_constants(dtype, variant):
     """Widths and head sizes no vector access or TMA box fits, a convolution of one tap, logits without a cap, a first layer
     that is a recurrence and a last one without a feed-forward."""
@@ -440,8 +440,12 @@ def test_other_sizes_and_constants(dtype, variant):
         cfg = D.make_cfg(width=100, vocab=131, taps=3, buckets=50, mul_prev=7, mul_cur=3, layers=[
             D.mlstm(heads=1, dim=34, vdim=50, mlp=D.dense(ff=44)), D.latent(heads=5, dim=10, rot_dim=6, rot_dims=2, vdim=14, kv_rank=18, mlp=D.moe(experts=3, top=3, ff=20, shared=12)),
             D.latent(second=True, heads=1, dim=130, rot_dim=2, vdim=6, kv_rank=22)])
-    else:
+    elif variant.startswith("one tap"):
         cfg = D.make_cfg(width=64, taps=1, softcap=0.0, layers=[D.latent(second=True, mlp=D.moe(experts=4, top=2, ff=32, shared=0)), D.mlstm(mlp=D.dense(ff=64))])
+    else:      # keys without a rotated part (tensor-core shapes: rows of 32 and 48), eight taps, a router that keeps all experts
+        cfg = D.make_cfg(width=128, taps=8, buckets=1, layers=[
+            D.latent(heads=4, dim=16, rot_dim=0, rot_dims=0, vdim=8, kv_rank=32, mlp=D.moe(experts=3, top=3, ff=16, shared=8)),
+            D.latent(second=True, heads=17, dim=8, rot_dim=16, rot_dims=16, vdim=8, kv_rank=32)])
     w = D.make_weights(cfg, 6)
     ids = _prompt(cfg, 45, 2)
     want = O.forward(cfg, w, ids).numpy()
